@@ -1,0 +1,158 @@
+/*
+ * b200k.h — C-ABI of libb200kernels.so: hand-written sm_100a kernels for the
+ * example kernels of kernelize-ai/triton-tenstorrent (vector add, sin,
+ * tensor-descriptor bf16 matmul, fused-epilogue matmul, fused-attention forward).
+ *
+ * Conventions
+ *   - Every pointer named below as "device" is a CUDA device pointer on the
+ *     CURRENT device; the caller owns all buffers.  `stream` is a cudaStream_t
+ *     passed as void* (NULL = legacy default stream).  Calls are asynchronous.
+ *   - Every function returns B200K_OK (0) or a negative b200k_status code; the
+ *     human-readable reason of the last failure on the calling thread is
+ *     returned by b200k_last_error().  No C++ exception crosses this boundary.
+ *   - The reference launches are synchronous (backend/driver.py:168 schedule.run(),
+ *     :361 ttrt.runtime.wait); callers that want that behaviour synchronise the
+ *     stream after the call.
+ */
+#ifndef B200K_H_
+#define B200K_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200k_status {
+  B200K_OK = 0,
+  B200K_ERR_INVALID_ARG = -1,   /* shape / stride / alignment / enum out of range   */
+  B200K_ERR_CUDA = -2,          /* a CUDA runtime or driver call failed              */
+  B200K_ERR_UNSUPPORTED = -3,   /* valid request this build has no kernel for        */
+  B200K_ERR_NO_DEVICE = -4,     /* no CUDA device / not an sm_100 device             */
+  B200K_ERR_DEVICE_TIMEOUT = -5 /* a bounded device-side wait gave up (see b200k_device_status) */
+} b200k_status;
+
+/* Bias operand of the fused matmul epilogue. */
+enum { B200K_BIAS_NONE = 0, B200K_BIAS_ROW_F32 = 1 /* bias[N] fp32 */, B200K_BIAS_FULL_BF16 = 2 /* bias[M,N] bf16 */ };
+/* Activation applied to the fp32 accumulator (after a fp32 bias add). */
+enum { B200K_ACT_NONE = 0, B200K_ACT_RELU = 1, B200K_ACT_LEAKY_RELU = 2 /* x>=0 ? x : 0.01x */ };
+
+/* Library ABI version (major*100+minor). */
+int b200k_version(void);
+/* Reason of the last failed call on this thread ("" if none). */
+const char* b200k_last_error(void);
+
+/*
+ * out[i] = x[i] + y[i], fp32, i in [0,n).
+ * Replaces: add_kernel, python/tutorials/01-vector-add.py:29-54 (launch :75).
+ * `block` is the reference's BLOCK_SIZE constexpr; it is validated (>0) and used only to
+ * report the equivalent reference grid — the result does not depend on it.
+ */
+int b200k_add_f32(const float* x, const float* y, float* out, int64_t n, int block, void* stream);
+
+/*
+ * out[i] = sinf(x[i]), fp32 (CUDA precise sinf, <= 1 ulp).
+ * Replaces: sin_kernel, examples/01-sin-kernel.py:17-29 (launch :36).
+ */
+int b200k_sin_f32(const float* x, float* out, int64_t n, int block, void* stream);
+
+/*
+ * out[i] = x[i] * y[i] + z[i] (one fused multiply-add is NOT used: product and sum are
+ * rounded separately like the reference's two Triton ops).
+ * Replaces: python/tutorials/01-vector-mul-add.py (x*y+z variant of add_kernel).
+ */
+int b200k_mul_add_f32(const float* x, const float* y, const float* z, float* out, int64_t n, int block, void* stream);
+
+/*
+ * C[M,N] = epilogue(A[M,K] . B[K,N]); A, B, C bf16 row-major with leading dimensions
+ * lda/ldb/ldc in ELEMENTS (multiples of 8; base pointers 16-byte aligned), fp32 accumulate,
+ * one round-to-nearest-even to bf16.
+ *   bias_kind = B200K_BIAS_NONE      : C = act(acc)
+ *   bias_kind = B200K_BIAS_ROW_F32   : C = bf16(act(acc + bias[n])), bias fp32[N]
+ *   bias_kind = B200K_BIAS_FULL_BF16 : bias bf16 [M,N] with leading dimension ldbias;
+ *        round_before_bias = 1 : C = bf16(float(bf16(act(acc))) + float(bias[m,n]))
+ *                                (python/tutorials/09-matmul-fused.py:139-146: add after the downcast)
+ *        round_before_bias = 0 : C = bf16(act(acc + float(bias[m,n])))
+ *                                (examples/matmul_fused/matmul_fused_add.cpp:49: add in fp32)
+ * Replaces: matmul_kernel_tma, examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py:105-143;
+ *           matmul_kernel_fused, python/tutorials/09-matmul-fused.py:105-148;
+ *           the contraction + leaky_relu of matmul_kernel, examples/matmul/03-matrix-multiplication.py:241-395.
+ * Loads outside [M,K]/[K,N] read zero and stores outside [M,N] are dropped, like the reference's
+ * tensor descriptors (npu/lib/Dialect/TritonTenstorrent/Transforms/ConvertTensorDescToLoadStore.cpp:57-105).
+ */
+int b200k_matmul_bf16(const void* A, const void* B, void* C, int M, int N, int K,
+                      int64_t lda, int64_t ldb, int64_t ldc,
+                      const void* bias, int bias_kind, int64_t ldbias,
+                      int act, int round_before_bias, void* stream);
+
+/*
+ * O = softmax(Q K^T * sm_scale [+ causal mask]) V per (batch, head); q,k,v,o bf16 contiguous
+ * [Z,H,N_CTX,D]; lse2[Z,H,N_CTX] fp32 receives m_i + log2(l_i) (base-2 log-sum-exp of the
+ * scaled scores), exactly the `M` tensor of the reference.  D must be 128 (64 also accepted if
+ * this build reports it via b200k_attn_supported), N_CTX a multiple of 128.
+ * Replaces: _attn_fwd / _attn_fwd_inner, examples/fused-attn/06-fused-attention.py:33-90,143-215
+ *           (host wrapper _attention.forward :224-273).
+ */
+int b200k_attn_fwd_bf16(const void* q, const void* k, const void* v, void* o, float* lse2,
+                        int Z, int H, int N_CTX, int D, int causal, float sm_scale, void* stream);
+/* 1 if b200k_attn_fwd_bf16 has a kernel for this (D, N_CTX), else 0. */
+int b200k_attn_supported(int D, int N_CTX);
+
+/*
+ * Generic launch mirroring the argument list the reference launcher builds
+ * (backend/driver.py:98-170 TTLauncher.__call__: constexprs dropped, tensors as pointers,
+ * TensorDescriptor flattened to base, shape.., strides.., padding flag, shape.., strides..).
+ * kernel_name is one of: "add_kernel", "sin_kernel", "mul_add_kernel", "matmul_kernel_tma",
+ * "matmul_kernel_fused", "_attn_fwd".  The grid is validated against the problem size
+ * implied by the arguments; it does not change the result.
+ */
+typedef enum b200k_arg_kind { B200K_ARG_PTR = 0, B200K_ARG_I32 = 1, B200K_ARG_I64 = 2, B200K_ARG_F32 = 3 } b200k_arg_kind;
+typedef struct b200k_arg {
+  int32_t kind; /* b200k_arg_kind */
+  int32_t _pad;
+  union {
+    void* ptr;
+    int32_t i32;
+    int64_t i64;
+    float f32;
+  } v;
+} b200k_arg;
+int b200k_launch(const char* kernel_name, int grid_x, int grid_y, int grid_z, void* stream,
+                 const b200k_arg* args, int nargs);
+
+/*
+ * Device properties in the shape of TTUtils.get_device_properties (backend/driver.py:76-82).
+ */
+typedef struct b200k_props {
+  int32_t multiprocessor_count;
+  int32_t max_shared_mem;     /* opt-in bytes per block */
+  int32_t max_num_regs;       /* 32-bit registers per SM */
+  int32_t warp_size;
+  int32_t cc_major, cc_minor;
+  int64_t total_mem;
+  char name[128];
+} b200k_props;
+int b200k_device_props(int device, b200k_props* out);
+
+/*
+ * Contiguous block range of worker `w` out of `workers` over `num_blocks` blocks:
+ * base = nb / W, rem = nb % W, worker w gets [w*base + min(w,rem), +base + (w<rem)).
+ * Replaces: the per-core partition of npu/lib/TritonNPUToTenstorrent/D2M/SPMDOpToD2M.cpp:53-113.
+ * Pure host arithmetic (no device needed).
+ */
+int b200k_block_range(int64_t num_blocks, int workers, int w, int64_t* block_start, int64_t* block_end);
+
+/*
+ * Reads (synchronously, after synchronising `stream`) the per-device status word that the
+ * matmul/attention kernels set when one of their bounded waits gives up.  *code receives 0 when
+ * healthy, else (site<<8 | role); the word is cleared.  Returns B200K_ERR_DEVICE_TIMEOUT if non-zero.
+ */
+int b200k_device_status(void* stream, uint32_t* code);
+
+/* Number of kernel launches issued by this library in the calling process (all threads). */
+int64_t b200k_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200K_H_ */

@@ -1,0 +1,80 @@
+// Host-side plumbing shared by the kernel launchers: error reporting for the C-ABI, per-device
+// information, the per-device status word, tensor-map (TMA descriptor) creation with a cache.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200k.h"
+
+namespace b200k {
+
+// Stores a printf-formatted message for b200k_last_error() (thread-local) and returns `code`.
+int set_error(int code, const char* fmt, ...);
+void clear_error();
+
+struct DeviceInfo {
+  int device;
+  int sm_count;
+  int cc_major, cc_minor;
+  int max_smem_optin;
+  uint32_t* status_word;  // device memory, 8 words, zero-initialised; word 0 = first failure code
+};
+// Information about the current device (created on first use; nullptr + error set on failure).
+const DeviceInfo* current_device_info();
+
+void count_launch();
+
+#define B200K_CHECK_LAUNCH(what)                                                                   \
+  do {                                                                                             \
+    cudaError_t e__ = cudaGetLastError();                                                          \
+    if (e__ != cudaSuccess) return set_error(B200K_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define B200K_CHECK_CUDA(expr)                                                                       \
+  do {                                                                                               \
+    cudaError_t e__ = (expr);                                                                        \
+    if (e__ != cudaSuccess) return set_error(B200K_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
+  } while (0)
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements,
+// box = box_inner x box_outer elements, 128-byte swizzle (box_inner * 2 bytes must be 128),
+// out-of-bounds reads fill with zero.  Cached per (base, dims, pitch, box).
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+
+// Kernel launchers (one translation unit each).
+int add_f32(const float* x, const float* y, float* out, int64_t n, cudaStream_t s);
+int sin_f32(const float* x, float* out, int64_t n, cudaStream_t s);
+int mul_add_f32(const float* x, const float* y, const float* z, float* out, int64_t n, cudaStream_t s);
+
+struct MatmulArgs {
+  const void* A;
+  const void* B;
+  void* C;
+  int M, N, K;
+  int64_t lda, ldb, ldc;
+  const void* bias;
+  int bias_kind;
+  int64_t ldbias;
+  int act;
+  int round_before_bias;
+};
+// status_override: device word the kernel reports bounded-wait failures to (nullptr = the
+// per-device word from current_device_info()).
+int matmul_bf16(const MatmulArgs& a, cudaStream_t s, uint32_t* status_override);
+
+struct AttnArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse2;
+  int Z, H, N_CTX, D;
+  int causal;
+  float sm_scale;
+};
+int attn_fwd_bf16(const AttnArgs& a, cudaStream_t s);
+int attn_supported(int D, int N_CTX);
+
+}  // namespace b200k

@@ -1,0 +1,391 @@
+// Persistent, warp-specialised bf16 matmul for sm_100a:  C = epilogue(A[M,K] . B[K,N]).
+//
+//   warp 0      TMA producer: A tile 128x64 (K-major) and B tile 64xBN (N-major, as B is row-major
+//               [K,N]) into a STAGES-deep shared-memory ring, 128-byte swizzle, completion on mbarriers
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x BN x 16 per instruction,
+//               fp32 accumulators in TMEM, two accumulator buffers so the epilogue of tile i overlaps
+//               the main loop of tile i+1) and tcgen05.commit to release ring slots / publish tiles
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32-lane quarter), fused bias /
+//               activation / rounding, swizzled staging in shared memory, TMA store of C
+//
+// The grid is one CTA per SM; CTA c walks tiles c, c+G, c+2G, ... of the reference's grouped tile
+// order (examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py:116-124), which is the
+// strided form of the persistent block loop the reference's compiler adds around the kernel
+// (cpu/lib/Dialect/TritonCPU/Transforms/MakePersistentKernel.cpp:144-198).
+// Contraction semantics follow matmul_kernel_tma (.ttnn.py:126-143): zero fill outside [M,K]/[K,N],
+// fp32 accumulation, one RNE downcast, stores outside [M,N] dropped.
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "launch.h"
+#include "ptx.cuh"
+
+namespace b200k {
+
+constexpr int MM_BM = 128;
+constexpr int MM_BK = 64;       // 64 bf16 = 128 bytes = one swizzle row
+constexpr int MM_UMMA_K = 16;
+constexpr int MM_THREADS = 192;
+constexpr int MM_EPI_WARPS = 4;
+constexpr int MM_A_STAGE_BYTES = MM_BM * MM_BK * 2;            // 16 KB
+constexpr int MM_B_BOX_BYTES = MM_BK * 64 * 2;                 // 8 KB: 64 k-rows x 64 n
+constexpr int MM_C_BUF_BYTES = 32 * 128;                       // 32 rows x 64 bf16
+constexpr int MM_C_STAGING_BYTES = MM_EPI_WARPS * 2 * MM_C_BUF_BYTES;  // 32 KB
+
+struct MatmulParams {
+  int M, N, K;
+  int num_pid_m, num_pid_n, group_m;
+  int num_tiles, num_kb;
+  const float* bias_row;      // [N] fp32 or nullptr
+  const uint16_t* bias_full;  // [M, ldbias] bf16 or nullptr
+  int64_t ldbias;
+  int act;
+  int round_before_bias;
+  uint32_t b_lbo, b_sbo, b_kstep;  // MN-major B descriptor strides (bytes)
+  uint32_t* status;
+};
+
+template <int BN, int STAGES>
+struct MatmulSmem {
+  static constexpr int B_STAGE_BYTES = (BN / 64) * MM_B_BOX_BYTES;
+  static constexpr int A_OFF = 0;
+  static constexpr int B_OFF = STAGES * MM_A_STAGE_BYTES;
+  static constexpr int C_OFF = B_OFF + STAGES * B_STAGE_BYTES;
+  static constexpr int BAR_OFF = C_OFF + MM_C_STAGING_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem_ptr, abort
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int TOTAL = BAR_OFF + BAR_BYTES + 1024;  // + slack to align the base to 1024
+};
+
+__device__ __forceinline__ void tile_coords(const MatmulParams& p, int tile, int& pid_m, int& pid_n) {
+  const int num_pid_in_group = p.group_m * p.num_pid_n;
+  const int group_id = tile / num_pid_in_group;
+  const int first_pid_m = group_id * p.group_m;
+  const int group_size_m = min(p.num_pid_m - first_pid_m, p.group_m);
+  const int in_group = tile - group_id * num_pid_in_group;
+  pid_m = first_pid_m + (in_group % group_size_m);
+  pid_n = in_group / group_size_m;
+}
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  if (act == B200K_ACT_RELU) return fmaxf(x, 0.f);
+  if (act == B200K_ACT_LEAKY_RELU) return x >= 0.f ? x : 0.01f * x;
+  return x;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(MM_THREADS, 1)
+matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                           const __grid_constant__ CUtensorMap tmap_c, const MatmulParams p) {
+  using L = MatmulSmem<BN, STAGES>;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+  constexpr uint32_t IDESC = umma_idesc_bf16_f32(MM_BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem + L::A_OFF;
+  uint8_t* smem_b = smem + L::B_OFF;
+  uint8_t* smem_c = smem + L::C_OFF;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  uint32_t* abort_smem = tmem_ptr_smem + 1;
+
+  const int warp_idx = threadIdx.x >> 5;  // warp-uniform
+  const uint32_t lane = lane_id();
+  WaitCtx ctx{abort_smem, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], MM_EPI_WARPS);
+    }
+    *abort_smem = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_c);
+  }
+  if (warp_idx == 1) {
+    tmem_alloc(tmem_ptr_smem, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp_idx == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int pid_m, pid_n;
+      tile_coords(p, tile, pid_m, pid_n);
+      const int m0 = pid_m * MM_BM, n0 = pid_n * BN;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = mbar_wait(&empty_bar[stage], phase ^ 1u, ctx, 1);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(&full_bar[stage], MM_A_STAGE_BYTES + L::B_STAGE_BYTES);
+          tma_load_2d(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, &full_bar[stage], kb * MM_BK, m0);
+#pragma unroll
+          for (int i = 0; i < BN / 64; ++i)
+            tma_load_2d(smem_b + stage * L::B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, &full_bar[stage],
+                        n0 + i * 64, kb * MM_BK);
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp_idx == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, ctx, 2);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = mbar_wait(&full_bar[stage], phase, ctx, 3);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(smem_a + stage * MM_A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + stage * L::B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < MM_BK / MM_UMMA_K; ++k) {
+            const uint64_t a_desc = umma_smem_desc_sw128(a_addr + k * (MM_UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = umma_smem_desc_sw128(b_addr + k * p.b_kstep, p.b_lbo, p.b_sbo);
+            umma_ss(d_tmem, a_desc, b_desc, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // slot reusable once these MMAs have read it
+          if (kb == p.num_kb - 1) umma_commit(&tmem_full_bar[acc]);  // accumulator complete
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int q = warp_idx & 3;  // TMEM lane quarter this warp may read
+    const int ew = warp_idx - 2;
+    uint8_t* my_stage = smem_c + ew * 2 * MM_C_BUF_BYTES;
+    int it = 0;
+    int buf = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+      int pid_m, pid_n;
+      tile_coords(p, tile, pid_m, pid_n);
+      const int m0 = pid_m * MM_BM, n0 = pid_n * BN;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(&tmem_full_bar[acc], acc_phase, ctx, 4);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + static_cast<int>(lane);
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_x32(t_row + c * 64, v0);
+        tmem_ld_x32(t_row + c * 64 + 32, v1);
+        tmem_wait_ld();
+        if (c == BN / 64 - 1) {
+          // whole accumulator is in registers / already stored: hand the TMEM buffer back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+        }
+        const int col0 = n0 + c * 64;
+        float f[64];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          f[j] = __uint_as_float(v0[j]);
+          f[32 + j] = __uint_as_float(v1[j]);
+        }
+        // ---- fused epilogue
+        if (p.bias_row != nullptr) {
+          if (col0 + 64 <= p.N) {
+            const float4* bp = reinterpret_cast<const float4*>(p.bias_row + col0);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float4 b = __ldg(bp + j);
+              f[4 * j + 0] += b.x;
+              f[4 * j + 1] += b.y;
+              f[4 * j + 2] += b.z;
+              f[4 * j + 3] += b.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+              if (col0 + j < p.N) f[j] += __ldg(p.bias_row + col0 + j);
+          }
+        }
+        float bfull[64];
+        const bool has_full = (p.bias_full != nullptr);
+        if (has_full) {
+          const bool row_ok = row < p.M;
+          const uint16_t* brow = p.bias_full + static_cast<int64_t>(row_ok ? row : 0) * p.ldbias + col0;
+          if (row_ok && col0 + 64 <= p.N && (p.ldbias & 7) == 0 &&
+              (reinterpret_cast<uintptr_t>(p.bias_full) & 15u) == 0) {
+            const uint4* bp = reinterpret_cast<const uint4*>(brow);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 b = __ldg(bp + j);
+              bfull[8 * j + 0] = bf16_bits_to_f32(b.x & 0xFFFFu);
+              bfull[8 * j + 1] = bf16_bits_to_f32(b.x >> 16);
+              bfull[8 * j + 2] = bf16_bits_to_f32(b.y & 0xFFFFu);
+              bfull[8 * j + 3] = bf16_bits_to_f32(b.y >> 16);
+              bfull[8 * j + 4] = bf16_bits_to_f32(b.z & 0xFFFFu);
+              bfull[8 * j + 5] = bf16_bits_to_f32(b.z >> 16);
+              bfull[8 * j + 6] = bf16_bits_to_f32(b.w & 0xFFFFu);
+              bfull[8 * j + 7] = bf16_bits_to_f32(b.w >> 16);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+              bfull[j] = (row_ok && col0 + j < p.N) ? bf16_bits_to_f32(__ldg(brow + j)) : 0.f;
+          }
+          if (!p.round_before_bias) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) f[j] += bfull[j];
+          }
+        }
+        if (p.act != B200K_ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) f[j] = apply_act(f[j], p.act);
+        }
+        uint32_t packed[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+        if (has_full && p.round_before_bias) {
+          // 16-bit add after the downcast: bf16(float(bf16(acc)) + float(bias))
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float lo = bf16_bits_to_f32(packed[j] & 0xFFFFu) + bfull[2 * j];
+            const float hi = bf16_bits_to_f32(packed[j] >> 16) + bfull[2 * j + 1];
+            packed[j] = pack_bf16x2(lo, hi);
+          }
+        }
+        // ---- staging buffer `buf` must no longer be read by the TMA store issued two chunks ago
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* dst = my_stage + buf * MM_C_BUF_BYTES + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = val;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (m0 + q * 32 < p.M && col0 < p.N)
+            tma_store_2d(&tmap_c, my_stage + buf * MM_C_BUF_BYTES, col0, m0 + q * 32);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp_idx == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host launcher
+// ---------------------------------------------------------------------------------------------
+template <int BN, int STAGES>
+static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_t stream, uint32_t* status) {
+  using L = MatmulSmem<BN, STAGES>;
+  static_assert(L::TOTAL <= 232448, "shared memory budget exceeded");
+  CUtensorMap ta, tb, tc;
+  int rc;
+  if ((rc = make_tmap_bf16_2d(&ta, a.A, a.K, a.M, a.lda, 64, MM_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tb, a.B, a.N, a.K, a.ldb, 64, MM_BK)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tc, a.C, a.N, a.M, a.ldc, 64, 32)) != 0) return rc;
+
+  MatmulParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.num_pid_m = (a.M + MM_BM - 1) / MM_BM;
+  p.num_pid_n = (a.N + BN - 1) / BN;
+  p.group_m = 8;
+  if (const char* g = getenv("B200K_MATMUL_GROUP_M")) { int v = atoi(g); if (v > 0) p.group_m = v; }
+  p.num_tiles = p.num_pid_m * p.num_pid_n;
+  p.num_kb = (a.K + MM_BK - 1) / MM_BK;
+  p.bias_row = (a.bias_kind == B200K_BIAS_ROW_F32) ? static_cast<const float*>(a.bias) : nullptr;
+  p.bias_full = (a.bias_kind == B200K_BIAS_FULL_BF16) ? static_cast<const uint16_t*>(a.bias) : nullptr;
+  p.ldbias = a.ldbias;
+  p.act = a.act;
+  p.round_before_bias = a.round_before_bias;
+  p.b_lbo = 64 * MM_BK * 2;  // next 64-column chunk of N = next 8 KB box
+  p.b_sbo = 1024;            // next group of 8 k-rows
+  p.b_kstep = MM_UMMA_K * 128;  // 16 k-rows of 128 bytes
+  if (const char* dbg = getenv("B200K_DEBUG_BDESC")) {  // bring-up aid: "lbo,sbo,kstep" in bytes
+    unsigned l = 0, sb = 0, ks = 0;
+    if (sscanf(dbg, "%u,%u,%u", &l, &sb, &ks) == 3) { p.b_lbo = l; p.b_sbo = sb; p.b_kstep = ks; }
+  }
+  p.status = status;
+
+  static bool attr_set = false;  // per instantiation; benign race (idempotent call)
+  if (!attr_set) {
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(matmul_bf16_tcgen05_kernel<BN, STAGES>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    attr_set = true;
+  }
+  int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  matmul_bf16_tcgen05_kernel<BN, STAGES><<<grid, MM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p);
+  count_launch();
+  B200K_CHECK_LAUNCH("matmul_bf16_tcgen05_kernel");
+  return B200K_OK;
+}
+
+int matmul_bf16(const MatmulArgs& a, cudaStream_t stream, uint32_t* status_override) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0) return set_error(B200K_ERR_INVALID_ARG, "matmul: M, N, K must be positive (got %d, %d, %d)", a.M, a.N, a.K);
+  if (a.A == nullptr || a.B == nullptr || a.C == nullptr) return set_error(B200K_ERR_INVALID_ARG, "matmul: null operand pointer");
+  if (a.lda < a.K || a.ldb < a.N || a.ldc < a.N) return set_error(B200K_ERR_INVALID_ARG, "matmul: leading dimension smaller than the row length");
+  if ((a.lda & 7) || (a.ldb & 7) || (a.ldc & 7))
+    return set_error(B200K_ERR_INVALID_ARG, "matmul: lda/ldb/ldc must be multiples of 8 elements (16-byte rows for TMA); got %lld, %lld, %lld",
+                     (long long)a.lda, (long long)a.ldb, (long long)a.ldc);
+  if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) | reinterpret_cast<uintptr_t>(a.C)) & 15u)
+    return set_error(B200K_ERR_INVALID_ARG, "matmul: A, B and C must be 16-byte aligned");
+  if (a.bias_kind < B200K_BIAS_NONE || a.bias_kind > B200K_BIAS_FULL_BF16) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad bias_kind %d", a.bias_kind);
+  if (a.act < B200K_ACT_NONE || a.act > B200K_ACT_LEAKY_RELU) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad act %d", a.act);
+  if (a.bias_kind != B200K_BIAS_NONE && a.bias == nullptr) return set_error(B200K_ERR_INVALID_ARG, "matmul: bias_kind %d needs a bias pointer", a.bias_kind);
+  if (a.bias_kind == B200K_BIAS_ROW_F32 && (reinterpret_cast<uintptr_t>(a.bias) & 15u))
+    return set_error(B200K_ERR_INVALID_ARG, "matmul: bias[N] must be 16-byte aligned");
+  if (a.bias_kind == B200K_BIAS_FULL_BF16 && a.ldbias < a.N) return set_error(B200K_ERR_INVALID_ARG, "matmul: ldbias smaller than N");
+  const DeviceInfo* dev = current_device_info();
+  if (dev == nullptr) return B200K_ERR_NO_DEVICE;
+  if (dev->cc_major != 10) return set_error(B200K_ERR_NO_DEVICE, "matmul: needs an sm_100 device (found sm_%d%d)", dev->cc_major, dev->cc_minor);
+  uint32_t* status = status_override ? status_override : dev->status_word;
+
+  // 128x256 tiles unless that leaves SMs idle and narrower tiles would not.
+  const int64_t tiles256 = static_cast<int64_t>((a.M + MM_BM - 1) / MM_BM) * ((a.N + 255) / 256);
+  bool narrow = (a.N <= 128) || (tiles256 < dev->sm_count);
+  if (const char* f = getenv("B200K_MATMUL_BN")) { int v = atoi(f); if (v == 128) narrow = true; if (v == 256) narrow = false; }
+  if (narrow) return launch_matmul<128, 6>(a, dev, stream, status);
+  return launch_matmul<256, 4>(a, dev, stream, status);
+}
+
+}  // namespace b200k

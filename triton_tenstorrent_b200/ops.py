@@ -1,0 +1,207 @@
+"""Host wrappers with the names and argument meaning of the reference examples' wrappers.
+
+Each function validates like the reference wrapper it mirrors, allocates the output with torch and
+calls the C-ABI (include/b200k.h) on the current CUDA stream.  Tensors may live on the GPU (the
+normal case) or on the host: host tensors are copied to the current device, computed there and the
+result is copied back, which is what the reference's D2M launcher does on every launch
+(backend/driver.py:350-381).  There is no CPU compute path.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+__all__ = ["add", "sin", "mul_add", "matmul", "matmul_tma", "matmul_fused", "matmul_tma_fused", "attention",
+           "attention_with_lse", "device_status"]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda():
+    if not torch.cuda.is_available():
+        raise RuntimeError("triton_tenstorrent_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
+
+
+def _to_device(t: torch.Tensor) -> torch.Tensor:
+    if t.is_cuda:
+        return t
+    _require_cuda()
+    return t.to("cuda", non_blocking=True)
+
+
+def _like_input(result: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
+    """Returns `result` on the device `ref` lives on (host inputs get a host result)."""
+    if ref.is_cuda:
+        return result
+    return result.to("cpu")
+
+
+def _elementwise_check(name, *tensors):
+    t0 = tensors[0]
+    for t in tensors:
+        if t.dtype != torch.float32:
+            raise TypeError(f"{name}: fp32 tensors expected, got {t.dtype}")
+        if t.shape != t0.shape:
+            raise ValueError(f"{name}: shape mismatch {tuple(t.shape)} vs {tuple(t0.shape)}")
+        if t.device != t0.device:
+            raise ValueError(f"{name}: tensors on different devices")
+
+
+def add(x: torch.Tensor, y: torch.Tensor, BLOCK_SIZE: int = 1024) -> torch.Tensor:
+    """out = x + y (fp32).  Mirrors add(), python/tutorials/01-vector-add.py:62-78."""
+    _elementwise_check("add", x, y)
+    lib = _lib.load()
+    xd, yd = _to_device(x).contiguous(), _to_device(y).contiguous()
+    out = torch.empty_like(xd)
+    with torch.cuda.device(xd.device):
+        _lib.check(lib.b200k_add_f32(xd.data_ptr(), yd.data_ptr(), out.data_ptr(), out.numel(), BLOCK_SIZE, _stream()))
+    return _like_input(out, x)
+
+
+def sin(x: torch.Tensor, BLOCK_SIZE: int = 1024) -> torch.Tensor:
+    """out = sin(x) (fp32).  Mirrors sin(), examples/01-sin-kernel.py:32-37."""
+    _elementwise_check("sin", x)
+    lib = _lib.load()
+    xd = _to_device(x).contiguous()
+    out = torch.empty_like(xd)
+    with torch.cuda.device(xd.device):
+        _lib.check(lib.b200k_sin_f32(xd.data_ptr(), out.data_ptr(), out.numel(), BLOCK_SIZE, _stream()))
+    return _like_input(out, x)
+
+
+def mul_add(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, BLOCK_SIZE: int = 1024) -> torch.Tensor:
+    """out = x * y + z (fp32, two roundings).  Mirrors python/tutorials/01-vector-mul-add.py."""
+    _elementwise_check("mul_add", x, y, z)
+    lib = _lib.load()
+    xd, yd, zd = (_to_device(t).contiguous() for t in (x, y, z))
+    out = torch.empty_like(xd)
+    with torch.cuda.device(xd.device):
+        _lib.check(lib.b200k_mul_add_f32(xd.data_ptr(), yd.data_ptr(), zd.data_ptr(), out.data_ptr(), out.numel(),
+                                         BLOCK_SIZE, _stream()))
+    return _like_input(out, x)
+
+
+_ACTIVATIONS = {"": _lib.ACT_NONE, None: _lib.ACT_NONE, "none": _lib.ACT_NONE, "relu": _lib.ACT_RELU,
+                "leaky_relu": _lib.ACT_LEAKY_RELU}
+
+
+def _row_major_2d(t: torch.Tensor, name: str) -> torch.Tensor:
+    """A 2-D bf16 view the TMA path accepts: unit inner stride, 16-byte aligned rows and base."""
+    if t.dim() != 2:
+        raise ValueError(f"{name}: 2-D tensor expected, got {t.dim()}-D")
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name}: bf16 expected, got {t.dtype}")
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0 or t.stride(0) < t.shape[1]:
+        if t.shape[1] % 8 != 0:
+            raise ValueError(f"{name}: the row length must be a multiple of 8 elements (16-byte rows, the same "
+                             f"constraint a tensor descriptor has); got shape {tuple(t.shape)}")
+        t = t.contiguous()
+    return t
+
+
+def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT_NONE, round_before_bias=0):
+    assert a.shape[1] == b.shape[0], "Incompatible dimensions"
+    assert a.dtype == b.dtype, "Incompatible dtypes"
+    lib = _lib.load()
+    ad, bd = _row_major_2d(_to_device(a), "a"), _row_major_2d(_to_device(b), "b")
+    M, K = ad.shape
+    _, N = bd.shape
+    if N % 8 != 0:
+        raise ValueError(f"matmul: N must be a multiple of 8 (16-byte rows of C); got {N}")
+    if c is None:
+        c = torch.empty((M, N), device=ad.device, dtype=torch.bfloat16)
+    bias_ptr, ldbias = 0, 0
+    if bias_kind == _lib.BIAS_ROW_F32:
+        bias = _to_device(bias).contiguous()
+        if bias.dtype != torch.float32 or bias.shape != (N,):
+            raise ValueError(f"bias must be fp32 [N={N}], got {bias.dtype} {tuple(bias.shape)}")
+        bias_ptr = bias.data_ptr()
+    elif bias_kind == _lib.BIAS_FULL_BF16:
+        bias = _to_device(bias)
+        assert bias.shape == (M, N), "Incompatible bias dimensions"
+        if bias.dtype != torch.bfloat16:
+            raise TypeError(f"bias must be bf16 [M,N], got {bias.dtype}")
+        if bias.stride(1) != 1:
+            bias = bias.contiguous()
+        bias_ptr, ldbias = bias.data_ptr(), bias.stride(0)
+    with torch.cuda.device(ad.device):
+        _lib.check(lib.b200k_matmul_bf16(ad.data_ptr(), bd.data_ptr(), c.data_ptr(), M, N, K, ad.stride(0), bd.stride(0),
+                                         c.stride(0), bias_ptr, bias_kind, ldbias, act, round_before_bias, _stream()))
+    return c
+
+
+def matmul_tma(a: torch.Tensor, b: torch.Tensor, warp_specialize: bool = True) -> torch.Tensor:
+    """C = A.B, bf16 in/out, fp32 accumulate.  Mirrors matmul_tma(a, b, warp_specialize),
+    examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py:146-173.  `warp_specialize` is accepted for
+    surface compatibility; the kernel is always warp-specialised."""
+    return _like_input(_matmul_call(a, b), a)
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "") -> torch.Tensor:
+    """C = act(A.B) with act in {"", "leaky_relu", "relu"} applied to the fp32 accumulator.
+    Mirrors matmul(a, b, activation), examples/matmul/03-matrix-multiplication.py:403-421 (operands are plain
+    row-major here; the 32x32 tile-major addressing of that file is a Tenstorrent memory layout)."""
+    assert a.is_contiguous(), "Matrix A must be contiguous"
+    if activation not in _ACTIVATIONS:
+        raise ValueError(f"unknown activation {activation!r}")
+    return _like_input(_matmul_call(a, b, act=_ACTIVATIONS[activation]), a)
+
+
+def matmul_fused(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor, activation: str = "relu") -> torch.Tensor:
+    """C = act(A.B + bias[N]) in one kernel: fp32 bias add and activation on the accumulator, one downcast.
+    This is the [N]-bias + ReLU epilogue of the fused-matmul workload."""
+    if activation not in _ACTIVATIONS:
+        raise ValueError(f"unknown activation {activation!r}")
+    return _like_input(_matmul_call(a, b, bias=bias, bias_kind=_lib.BIAS_ROW_F32, act=_ACTIVATIONS[activation]), a)
+
+
+def matmul_tma_fused(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor, warp_specialize: bool = True,
+                     round_before_bias: bool = True) -> torch.Tensor:
+    """C = (A.B downcast) + bias[M,N].  Mirrors matmul_tma(a, b, bias, warp_specialize),
+    python/tutorials/09-matmul-fused.py:151-181: the bias tile is added after the downcast (:139-146).
+    round_before_bias=False gives the single rounding of the C++ golden (matmul_fused_add.cpp:49)."""
+    return _like_input(_matmul_call(a, b, bias=bias, bias_kind=_lib.BIAS_FULL_BF16,
+                                    round_before_bias=1 if round_before_bias else 0), a)
+
+
+def attention_with_lse(q, k, v, causal, sm_scale, warp_specialize: bool = True):
+    """Returns (O, M): the attention output and the fp32 base-2 log-sum-exp rows the reference saves for
+    its backward (examples/fused-attn/06-fused-attention.py:238,269)."""
+    HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
+    assert HEAD_DIM_K in {16, 32, 64, 128, 256}
+    if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape:
+        raise ValueError("attention: q, k, v must be [Z, H, N_CTX, HEAD_DIM] with equal shapes")
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise TypeError("attention: bf16 tensors expected")
+    lib = _lib.load()
+    Z, H, N_CTX, D = q.shape
+    if not lib.b200k_attn_supported(D, N_CTX):
+        raise NotImplementedError(f"attention: no sm_100a kernel for HEAD_DIM={D}, N_CTX={N_CTX} "
+                                  "(HEAD_DIM 128 and N_CTX a multiple of 128 are built)")
+    qd, kd, vd = (_to_device(t).contiguous() for t in (q, k, v))
+    o = torch.empty_like(qd)
+    M = torch.empty((Z, H, N_CTX), device=qd.device, dtype=torch.float32)
+    with torch.cuda.device(qd.device):
+        _lib.check(lib.b200k_attn_fwd_bf16(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), M.data_ptr(),
+                                           Z, H, N_CTX, D, 1 if causal else 0, float(sm_scale), _stream()))
+    return _like_input(o, q), _like_input(M, q)
+
+
+def attention(q, k, v, causal, sm_scale, warp_specialize: bool = True) -> torch.Tensor:
+    """O = softmax(Q K^T sm_scale [+ causal mask]) V.  Mirrors _attention.forward / _attention.apply,
+    examples/fused-attn/06-fused-attention.py:224-273."""
+    return attention_with_lse(q, k, v, causal, sm_scale, warp_specialize)[0]
+
+
+def device_status() -> int:
+    """Synchronises the current stream and returns the device status word (0 = healthy); raises
+    B200KError if one of the kernels' bounded waits gave up."""
+    import ctypes
+    lib = _lib.load()
+    code = ctypes.c_uint32(0)
+    _lib.check(lib.b200k_device_status(_stream(), ctypes.byref(code)))
+    return code.value
