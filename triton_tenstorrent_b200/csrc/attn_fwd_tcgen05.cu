@@ -1,5 +1,494 @@
+// Fused attention forward for sm_100a: O = softmax(Q K^T * sm_scale [+ causal mask]) V, bf16 in/out,
+// HEAD_DIM 128, blockwise online softmax in the base-2 domain exactly like the reference kernel
+// (examples/fused-attn/06-fused-attention.py:33-90 inner loop, :143-215 prologue/epilogue).
+//
+// One CTA owns a pair of adjacent 128-row Q tiles of one (batch, head) and walks the K/V blocks of
+// 128 keys once for both:
+//   warps 0-3   softmax group of Q tile 0     warps 4-7   softmax group of Q tile 1
+//   warp 8      TMA producer (Q tiles, K/V ring of 32 KB slots in the order K0 V0 K1 V1 ...)
+//   warp 9      tensor-memory owner and tcgen05.mma issuer
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  S = Q K^T is produced
+// by an SS MMA; each softmax thread owns one row (tcgen05.ld 32x32b), so row max / row sum need no
+// cross-thread exchange; P is rounded to bf16 (the reference's p.to(dtype), :81) and written back
+// over the first 64 columns of S; O += P V is a TS MMA with P read from tensor memory and V
+// consumed row-major (MN-major B operand).  While one tile's softmax runs, the tensor pipe works on
+// the other tile.
+//
+// Rescaling of O: the reference multiplies the accumulator by alpha = 2^(m_old - m_new) in every
+// block (:66-78).  Here the running maximum used for the exponentials is only advanced when it
+// would grow by more than 2^8 for some row of the warp (a warp vote), and O (in tensor memory) is
+// rescaled only then; P and l are scaled by the same power of two, so O/l is unchanged up to fp32
+// rounding, and M = m + log2(l) is unchanged.
+#include <math.h>
+#include <stdlib.h>
+
 #include "launch.h"
+#include "ptx.cuh"
+
 namespace b200k {
-int attn_supported(int D, int N_CTX) { return 0; }
-int attn_fwd_bf16(const AttnArgs& a, cudaStream_t s) { return set_error(B200K_ERR_UNSUPPORTED, "attention: not built yet"); }
+
+constexpr int AT_BM = 128;            // rows per Q tile
+constexpr int AT_BN = 128;            // keys per K/V block
+constexpr int AT_D = 128;             // head dimension
+constexpr int AT_THREADS = 320;
+constexpr int AT_TILE_BYTES = AT_BM * AT_D * 2;  // 32 KB: two 16 KB boxes of 64 columns
+constexpr int AT_BOX_BYTES = 16384;
+constexpr int AT_NSLOT = 5;           // K/V ring slots
+constexpr int AT_Q_OFF = 0;
+constexpr int AT_KV_OFF = 2 * AT_TILE_BYTES;
+constexpr int AT_BAR_OFF = AT_KV_OFF + AT_NSLOT * AT_TILE_BYTES;
+constexpr int AT_NBAR = 2 + 2 + 2 * AT_NSLOT + 2 + 2 + 2;
+constexpr int AT_SMEM_TOTAL = AT_BAR_OFF + AT_NBAR * 8 + 16 + 1024;
+static_assert(AT_SMEM_TOTAL <= 232448, "attention shared memory budget exceeded");
+
+constexpr float AT_RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct AttnParams {
+  int ZH, N_CTX;
+  int num_mblk, num_pairs, num_items;
+  int causal;
+  float qk_scale;  // sm_scale * 1.44269504 (fp32 product, as the reference computes it)
+  float* lse2;
+  uint32_t* status;
+};
+
+struct AttnItem {
+  int hz;
+  int mblk[2];
+  int nblk[2];  // K/V blocks each tile consumes (0 = tile absent)
+  int n;        // K/V blocks loaded
+};
+
+__device__ __forceinline__ AttnItem attn_item(const AttnParams& p, int item) {
+  AttnItem it;
+  it.hz = item / p.num_pairs;
+  int pr = item - it.hz * p.num_pairs;
+  if (p.causal) pr = p.num_pairs - 1 - pr;  // longest rows first
+  it.mblk[0] = 2 * pr;
+  it.mblk[1] = 2 * pr + 1;
+  const bool valid1 = it.mblk[1] < p.num_mblk;
+  it.nblk[0] = p.causal ? it.mblk[0] + 1 : p.num_mblk;
+  it.nblk[1] = valid1 ? (p.causal ? it.mblk[1] + 1 : p.num_mblk) : 0;
+  it.n = it.nblk[1] > it.nblk[0] ? it.nblk[1] : it.nblk[0];
+  return it;
 }
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                             const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                             const AttnParams p) {
+  constexpr uint32_t IDESC_S = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);   // Q (K-major) x K^T (K-major)
+  constexpr uint32_t IDESC_PV = umma_idesc_bf16_f32(AT_BM, AT_D, 0, 1);   // P (TMEM) x V (N-major)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_q = smem + AT_Q_OFF;
+  uint8_t* smem_kv = smem + AT_KV_OFF;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + AT_BAR_OFF);
+  uint64_t* q_empty = q_full + 2;
+  uint64_t* kv_full = q_empty + 2;
+  uint64_t* kv_empty = kv_full + AT_NSLOT;
+  uint64_t* s_full = kv_empty + AT_NSLOT;
+  uint64_t* p_full = s_full + 2;
+  uint64_t* o_full = p_full + 2;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(o_full + 2);
+  uint32_t* abort_smem = tmem_ptr_smem + 1;
+
+  const int warp_idx = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  WaitCtx ctx{abort_smem, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&q_full[t], 1);
+      mbar_init(&q_empty[t], 4);
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 4);
+      mbar_init(&o_full[t], 1);
+    }
+    for (int s = 0; s < AT_NSLOT; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    *abort_smem = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_o);
+  }
+  if (warp_idx == 9) {
+    tmem_alloc(tmem_ptr_smem, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp_idx == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    int slot = 0;
+    uint32_t slot_phase = 0;
+    uint32_t q_loads[2] = {0, 0};
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      const AttnItem it = attn_item(p, item);
+      const int row_base = it.hz * p.N_CTX;
+      for (int step = 0; ok && step < 2 * it.n; ++step) {
+        // Q tiles are interleaved with the first K/V blocks: Q0 K0 Q1 V0 K1 V1 ...
+        if (step < 2 && it.nblk[step] > 0) {
+          const int t = step;
+          ok = mbar_wait(&q_empty[t], (q_loads[t] & 1u) ^ 1u, ctx, 10);
+          if (!ok) break;
+          if (lane == 0) {
+            mbar_expect_tx(&q_full[t], AT_TILE_BYTES);
+            const int row = row_base + it.mblk[t] * AT_BM;
+            tma_load_2d(smem_q + t * AT_TILE_BYTES, &tmap_q, &q_full[t], 0, row);
+            tma_load_2d(smem_q + t * AT_TILE_BYTES + AT_BOX_BYTES, &tmap_q, &q_full[t], 64, row);
+          }
+          __syncwarp();
+          ++q_loads[t];
+        }
+        const int j = step >> 1;
+        const bool is_v = (step & 1) != 0;
+        ok = mbar_wait(&kv_empty[slot], slot_phase ^ 1u, ctx, 11);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(&kv_full[slot], AT_TILE_BYTES);
+          const CUtensorMap* tm = is_v ? &tmap_v : &tmap_k;
+          const int row = row_base + j * AT_BN;
+          uint8_t* dst = smem_kv + slot * AT_TILE_BYTES;
+          tma_load_2d(dst, tm, &kv_full[slot], 0, row);
+          tma_load_2d(dst + AT_BOX_BYTES, tm, &kv_full[slot], 64, row);
+        }
+        __syncwarp();
+        if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
+      }
+    }
+  } else if (warp_idx == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    int slot = 0;                 // next ring slot to consume (K0 V0 K1 V1 ...)
+    uint32_t slot_phase = 0;
+    uint32_t q_cnt[2] = {0, 0};   // Q tiles consumed per tile index
+    uint32_t p_cnt[2] = {0, 0};   // P blocks consumed per tile index
+    bool ok = true;
+    const uint32_t q_addr[2] = {smem_u32(smem_q), smem_u32(smem_q + AT_TILE_BYTES)};
+    const uint32_t kv_addr0 = smem_u32(smem_kv);
+
+    auto issue_s = [&](int t, uint32_t k_addr) {
+      // S_t = Q_t K^T : 8 MMAs of K = 16 over the head dimension (two 64-column boxes)
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < AT_D / 16; ++k) {
+          const uint32_t off = (k >> 2) * AT_BOX_BYTES + (k & 3) * 32;
+          umma_ss(tmem_base + t * 128, umma_smem_desc_sw128(q_addr[t] + off, 16, 1024),
+                  umma_smem_desc_sw128(k_addr + off, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[t]);
+      }
+      __syncwarp();
+    };
+    auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
+      // O_t (+)= P_t V : 8 MMAs of K = 16 over the keys; P_t is bf16 in TMEM (8 columns per K step)
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < AT_BN / 16; ++k)
+          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+                  umma_smem_desc_sw128(v_addr + k * 2048, AT_BOX_BYTES, 1024), IDESC_PV,
+                  (accumulate || k > 0) ? 1u : 0u);
+      }
+      __syncwarp();
+    };
+
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      const AttnItem it = attn_item(p, item);
+      // ---- block 0 scores
+      ok = mbar_wait(&kv_full[slot], slot_phase, ctx, 20);
+      if (!ok) break;
+      uint32_t k_addr = kv_addr0 + slot * AT_TILE_BYTES;
+      int k_slot = slot;
+      if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
+      for (int t = 0; ok && t < 2; ++t) {
+        if (it.nblk[t] == 0) continue;
+        ok = mbar_wait(&q_full[t], q_cnt[t] & 1u, ctx, 21);
+        if (!ok) break;
+        ++q_cnt[t];
+        tc_fence_after();
+        issue_s(t, k_addr);
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit(&kv_empty[k_slot]);
+      __syncwarp();
+      // ---- main loop
+      for (int j = 0; ok && j < it.n; ++j) {
+        ok = mbar_wait(&kv_full[slot], slot_phase, ctx, 22);  // V_j
+        if (!ok) break;
+        const uint32_t v_addr = kv_addr0 + slot * AT_TILE_BYTES;
+        const int v_slot = slot;
+        if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
+        const bool have_next = (j + 1 < it.n);
+        bool next_k_ready = false;
+        for (int t = 0; ok && t < 2; ++t) {
+          if (j < it.nblk[t]) {
+            ok = mbar_wait(&p_full[t], p_cnt[t] & 1u, ctx, 23);
+            if (!ok) break;
+            ++p_cnt[t];
+            tc_fence_after();
+            issue_pv(t, v_addr, j > 0);
+            if (j == it.nblk[t] - 1) {
+              if (lane == 0) umma_commit(&o_full[t]);
+              __syncwarp();
+            }
+          }
+          if (t == 1) {
+            if (lane == 0) umma_commit(&kv_empty[v_slot]);  // every PV of block j has been issued
+            __syncwarp();
+          }
+          if (j + 1 < it.nblk[t]) {
+            if (!next_k_ready) {
+              ok = mbar_wait(&kv_full[slot], slot_phase, ctx, 24);  // K_{j+1}
+              if (!ok) break;
+              next_k_ready = true;
+              tc_fence_after();
+            }
+            issue_s(t, kv_addr0 + slot * AT_TILE_BYTES);
+          }
+        }
+        if (!ok) break;
+        if (have_next) {
+          if (!next_k_ready) {  // no tile used K_{j+1} (cannot happen while have_next, kept for safety)
+            ok = mbar_wait(&kv_full[slot], slot_phase, ctx, 25);
+            if (!ok) break;
+          }
+          if (lane == 0) umma_commit(&kv_empty[slot]);
+          __syncwarp();
+          if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups (warps 0..7)
+    const int t = warp_idx >> 2;        // Q tile of this group
+    const int q = warp_idx & 3;         // TMEM lane quarter
+    const int r = q * 32 + static_cast<int>(lane);  // row within the tile
+    const uint32_t lane_field = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_field + t * 128;        // S_t / P_t
+    const uint32_t t_o = tmem_base + lane_field + 256 + t * 128;  // O_t
+    uint8_t* stage = smem_q + t * AT_TILE_BYTES;                  // O staging reuses the Q tile
+    const float scale = p.qk_scale;
+    uint32_t blk_cnt = 0, item_cnt = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      const AttnItem it = attn_item(p, item);
+      const int n_me = it.nblk[t];
+      if (n_me == 0) continue;
+      float m_used = -INFINITY;
+      float l = 0.f;
+      for (int j = 0; j < n_me; ++j) {
+        ok = mbar_wait(&s_full[t], blk_cnt & 1u, ctx, 30);
+        if (!ok) break;
+        ++blk_cnt;
+        tc_fence_after();
+        uint32_t s0[32], s1[32], s2[32], s3[32];
+        tmem_ld_x32(t_s + 0, s0);
+        tmem_ld_x32(t_s + 32, s1);
+        tmem_ld_x32(t_s + 64, s2);
+        tmem_ld_x32(t_s + 96, s3);
+        tmem_wait_ld();
+        if (p.causal && j == n_me - 1) {
+          // diagonal block: key index > query index is masked (reference adds -1e6 before the max;
+          // after exp2 both give exactly 0)
+          const uint32_t ninf = 0xFF800000u;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            if (c > r) s0[c] = ninf;
+            if (c + 32 > r) s1[c] = ninf;
+            if (c + 64 > r) s2[c] = ninf;
+            if (c + 96 > r) s3[c] = ninf;
+          }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
+          mx1 = fmaxf(mx1, __uint_as_float(s1[c]));
+          mx2 = fmaxf(mx2, __uint_as_float(s2[c]));
+          mx3 = fmaxf(mx3, __uint_as_float(s3[c]));
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        const float m_new = fmaxf(m_used, mx * scale);
+        const bool need = (m_new - m_used) > AT_RESCALE_THRESHOLD;  // true for j == 0 (m_used = -inf)
+        if (__any_sync(0xFFFFFFFFu, need)) {
+          const float alpha = (j == 0) ? 0.f : ex2_approx(m_used - m_new);
+          m_used = m_new;
+          l *= alpha;
+          if (j > 0) {
+            // the PV MMA of block j-1 has completed (its completion precedes s_full of block j)
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint32_t o[32];
+              tmem_ld_x32(t_o + c4 * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+              tmem_st_x32(t_o + c4 * 32, o);
+            }
+          }
+        }
+        const float neg_m = -m_used;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float a0 = ex2_approx(fmaf(__uint_as_float(s0[2 * c]), scale, neg_m));
+            const float a1 = ex2_approx(fmaf(__uint_as_float(s0[2 * c + 1]), scale, neg_m));
+            const float b0 = ex2_approx(fmaf(__uint_as_float(s1[2 * c]), scale, neg_m));
+            const float b1 = ex2_approx(fmaf(__uint_as_float(s1[2 * c + 1]), scale, neg_m));
+            sum0 += a0; sum1 += a1; sum2 += b0; sum3 += b1;
+            pk[c] = pack_bf16x2(a0, a1);
+            pk[16 + c] = pack_bf16x2(b0, b1);
+          }
+          tmem_st_x32(t_s, pk);
+        }
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float a0 = ex2_approx(fmaf(__uint_as_float(s2[2 * c]), scale, neg_m));
+            const float a1 = ex2_approx(fmaf(__uint_as_float(s2[2 * c + 1]), scale, neg_m));
+            const float b0 = ex2_approx(fmaf(__uint_as_float(s3[2 * c]), scale, neg_m));
+            const float b1 = ex2_approx(fmaf(__uint_as_float(s3[2 * c + 1]), scale, neg_m));
+            sum0 += a0; sum1 += a1; sum2 += b0; sum3 += b1;
+            pk[c] = pack_bf16x2(a0, a1);
+            pk[16 + c] = pack_bf16x2(b0, b1);
+          }
+          tmem_st_x32(t_s + 32, pk);
+        }
+        l += (sum0 + sum1) + (sum2 + sum3);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t]);
+      }
+      if (!ok) break;
+      // ---- epilogue: O / l -> bf16 -> swizzled staging (the Q tile's buffer) -> TMA store; M = m + log2(l)
+      ok = mbar_wait(&o_full[t], item_cnt & 1u, ctx, 31);
+      if (!ok) break;
+      ++item_cnt;
+      tc_fence_after();
+      const float inv_l = 1.0f / l;
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t o[32];
+        tmem_ld_x32(t_o + c4 * 32, o);
+        tmem_wait_ld();
+        uint8_t* row_ptr = stage + (c4 >> 1) * AT_BOX_BYTES + r * 128;
+        const int chunk0 = (c4 & 1) * 4;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint4 val;
+          val.x = pack_bf16x2(__uint_as_float(o[8 * jj + 0]) * inv_l, __uint_as_float(o[8 * jj + 1]) * inv_l);
+          val.y = pack_bf16x2(__uint_as_float(o[8 * jj + 2]) * inv_l, __uint_as_float(o[8 * jj + 3]) * inv_l);
+          val.z = pack_bf16x2(__uint_as_float(o[8 * jj + 4]) * inv_l, __uint_as_float(o[8 * jj + 5]) * inv_l);
+          val.w = pack_bf16x2(__uint_as_float(o[8 * jj + 6]) * inv_l, __uint_as_float(o[8 * jj + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(row_ptr + (((chunk0 + jj) ^ (r & 7)) << 4)) = val;
+        }
+      }
+      tc_fence_before();
+      const int64_t out_row = static_cast<int64_t>(it.hz) * p.N_CTX + it.mblk[t] * AT_BM;
+      p.lse2[out_row + r] = m_used + log2f(l);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int y = static_cast<int>(out_row) + q * 32;
+        tma_store_2d(&tmap_o, stage + q * 32 * 128, 0, y);
+        tma_store_2d(&tmap_o, stage + AT_BOX_BYTES + q * 32 * 128, 64, y);
+        tma_store_commit();
+        tma_store_wait_read<0>();
+        mbar_arrive(&q_empty[t]);  // the Q buffer may be refilled
+      }
+      __syncwarp();
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // -------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp_idx == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int attn_supported(int D, int N_CTX) { return (D == AT_D && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0; }
+
+static int pick_grid(int sm_count, int num_items, int num_pairs, bool causal) {
+  int grid = num_items < sm_count ? num_items : sm_count;
+  if (causal && num_pairs > 1 && grid > 1) {
+    // Items are strided over CTAs; with a stride that shares a factor with the number of row pairs
+    // per head a CTA would only ever see a few of the (unequally long) causal row positions.
+    auto gcd = [](int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; };
+    while (grid > 1 && gcd(grid, num_pairs) != 1) --grid;
+  }
+  return grid;
+}
+
+int attn_fwd_bf16(const AttnArgs& a, cudaStream_t stream) {
+  if (a.Z <= 0 || a.H <= 0 || a.N_CTX <= 0) return set_error(B200K_ERR_INVALID_ARG, "attention: Z, H, N_CTX must be positive");
+  if (!attn_supported(a.D, a.N_CTX))
+    return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 128, N_CTX multiple of 128)", a.D, a.N_CTX);
+  if (a.q == nullptr || a.k == nullptr || a.v == nullptr || a.o == nullptr || a.lse2 == nullptr)
+    return set_error(B200K_ERR_INVALID_ARG, "attention: null pointer");
+  if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
+       reinterpret_cast<uintptr_t>(a.o)) & 15u)
+    return set_error(B200K_ERR_INVALID_ARG, "attention: q, k, v, o must be 16-byte aligned");
+  const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
+  if (rows > 0x7FFFFFFF) return set_error(B200K_ERR_INVALID_ARG, "attention: Z*H*N_CTX exceeds 2^31-1 rows");
+  if (!(a.sm_scale > 0.f) || !isfinite(a.sm_scale)) return set_error(B200K_ERR_INVALID_ARG, "attention: sm_scale must be positive and finite");
+  const DeviceInfo* dev = current_device_info();
+  if (dev == nullptr) return B200K_ERR_NO_DEVICE;
+  if (dev->cc_major != 10) return set_error(B200K_ERR_NO_DEVICE, "attention: needs an sm_100 device (found sm_%d%d)", dev->cc_major, dev->cc_minor);
+
+  CUtensorMap tq, tk, tv, to;
+  int rc;
+  if ((rc = make_tmap_bf16_2d(&tq, a.q, AT_D, rows, AT_D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tk, a.k, AT_D, rows, AT_D, 64, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tv, a.v, AT_D, rows, AT_D, 64, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&to, a.o, AT_D, rows, AT_D, 64, 32)) != 0) return rc;
+
+  AttnParams p;
+  p.ZH = a.Z * a.H;
+  p.N_CTX = a.N_CTX;
+  p.num_mblk = a.N_CTX / AT_BM;
+  p.num_pairs = (p.num_mblk + 1) / 2;
+  p.num_items = p.ZH * p.num_pairs;
+  p.causal = a.causal ? 1 : 0;
+  p.qk_scale = a.sm_scale * 1.44269504f;
+  p.lse2 = a.lse2;
+  p.status = dev->status_word;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          AT_SMEM_TOTAL));
+    attr_set = true;
+  }
+  int grid = pick_grid(dev->sm_count, p.num_items, p.num_pairs, p.causal != 0);
+  if (const char* g = getenv("B200K_ATTN_GRID")) { int v = atoi(g); if (v > 0 && v <= p.num_items) grid = v; }
+  attn_fwd_bf16_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_TOTAL, stream>>>(tq, tk, tv, to, p);
+  count_launch();
+  B200K_CHECK_LAUNCH("attn_fwd_bf16_tcgen05_kernel");
+  return B200K_OK;
+}
+
+}  // namespace b200k
