@@ -1,0 +1,96 @@
+"""The CPU oracle against the golden vectors made by executing the reference's kernel sources
+(tests/golden/make_golden.py).  Runs without a GPU."""
+import numpy as np
+import pytest
+import torch
+
+import golden_inputs as gi
+from oracle import cpu_oracle as oracle
+
+
+def _bf16(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def bf16_ulp_diff(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Element-wise distance in bf16 units in the last place."""
+    ia = a.contiguous().view(torch.int16).to(torch.int32)
+    ib = b.contiguous().view(torch.int16).to(torch.int32)
+    ia = torch.where(ia < 0, -(ia & 0x7FFF), ia)
+    ib = torch.where(ib < 0, -(ib & 0x7FFF), ib)
+    return (ia - ib).abs()
+
+
+@pytest.mark.parametrize("n", gi.ADD_SIZES)
+def test_add_bit_exact(golden_dir, n):
+    g = np.load(golden_dir / "add.npz")
+    x, y = gi.add_inputs(n)
+    assert str(g[f"in_sha_{n}"]) == gi.digest(x, y), "input generator drifted from the golden vectors"
+    for workers in (1, 3, 0):
+        out = oracle.add(x, y, block=1024, workers=workers)
+        assert np.array_equal(out.numpy(), g[f"out_{n}"])
+
+
+@pytest.mark.parametrize("n", gi.SIN_SIZES)
+def test_sin_within_2ulp(golden_dir, n):
+    g = np.load(golden_dir / "sin.npz")
+    x = gi.sin_inputs(n)
+    assert str(g[f"in_sha_{n}"]) == gi.digest(x)
+    golden = torch.from_numpy(g[f"out_{n}"])
+    out = oracle.sin(x)
+    truth = oracle.sin_correctly_rounded(x)
+    assert oracle.ulp_diff_f32(out, truth) <= 1          # libm sinf
+    assert oracle.ulp_diff_f32(golden, truth) <= 1       # the interpreter's np.sin in fp32
+    assert oracle.ulp_diff_f32(out, golden) <= 2
+
+
+@pytest.mark.parametrize("shape", gi.MATMUL_SHAPES)
+def test_matmul_golden(golden_dir, shape):
+    M, N, K = shape
+    g = np.load(golden_dir / "matmul.npz")
+    a, b = gi.matmul_inputs(M, N, K)
+    tag = f"{M}x{N}x{K}"
+    assert str(g[f"in_sha_{tag}"]) == gi.digest(a, b)
+    golden = _bf16(g[f"c_{tag}"])
+    out = oracle.golden_matmul(a, b)
+    # same products, fp32 accumulation in a different order: results agree except for rare
+    # round-to-nearest ties broken the other way (1 bf16 ulp)
+    d = bf16_ulp_diff(out, golden)
+    assert int(d.max()) <= 1
+    assert float((d > 0).float().mean()) < 2e-3
+    assert oracle.rel_frobenius(out.float(), golden.float()) < 1e-3
+    naive = oracle.golden_matmul_naive(a, b)
+    assert torch.equal(naive.view(torch.int16), out.view(torch.int16))  # staging B does not change the sum order
+
+
+@pytest.mark.parametrize("shape", gi.FUSED_SHAPES)
+def test_matmul_fused_golden_fp16(golden_dir, shape):
+    M, N, K = shape
+    g = np.load(golden_dir / "matmul_fused.npz")
+    a, b, bias = gi.fused_inputs(M, N, K, dtype=torch.float16)
+    tag = f"{M}x{N}x{K}"
+    assert str(g[f"in_sha_{tag}"]) == gi.digest(a, b, bias)
+    golden = torch.from_numpy(g[f"c_{tag}"])
+    out = oracle.golden_matmul(a, b, bias=bias, mode=2)  # add after the downcast, like the Triton kernel
+    diff = (out.float() - golden.float()).abs()
+    # one fp16 ulp of the largest magnitude involved
+    assert float(diff.max()) <= float(golden.float().abs().max()) * 2 ** -10
+    assert float((diff > 0).float().mean()) < 5e-3
+    # the C++ golden's single rounding differs from the kernel's double rounding only by rounding noise
+    single = oracle.golden_matmul(a, b, bias=bias, mode=1)
+    assert oracle.rel_frobenius(single.float(), golden.float()) < 1e-3
+
+
+@pytest.mark.parametrize("case", gi.ATTN_CASES)
+def test_attention_golden(golden_dir, case):
+    Z, H, S, D, causal, BM, BN = case
+    g = np.load(golden_dir / "attention.npz")
+    q, k, v = gi.attn_inputs(Z, H, S, D)
+    tag = f"{Z}x{H}x{S}x{D}_{'c' if causal else 'n'}_{BM}x{BN}"
+    assert str(g[f"in_sha_{tag}"]) == gi.digest(q, k, v)
+    golden_o, golden_m = _bf16(g[f"o_{tag}"]), torch.from_numpy(g[f"M_{tag}"])
+    o, m = oracle.attention(q, k, v, causal, D ** -0.5, BLOCK_M=BM, BLOCK_N=BN)
+    # identical algorithm and rounding points; only fp32 summation order inside the dots differs
+    assert float((o.float() - golden_o.float()).abs().max()) <= 2 ** -6   # <= 1 bf16 ulp at |o| < 4
+    assert float((bf16_ulp_diff(o, golden_o) > 0).float().mean()) < 0.02
+    assert float((m - golden_m).abs().max()) < 1e-5
