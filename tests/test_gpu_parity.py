@@ -1,0 +1,347 @@
+"""Parity of the CUDA path (called through the C-ABI) with the CPU oracle and with the golden vectors
+made from the reference's kernel sources.  Tolerances are the workload's:
+  add: bit-exact;  sin: <= 2 ulp;  matmul: relative Frobenius error <= 1e-2;  attention: max-abs <= 2e-2.
+"""
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import golden_inputs as gi
+from oracle import cpu_oracle as oracle
+from triton_tenstorrent_b200 import _lib, kernels, ops
+from triton_tenstorrent_b200.tensor_descriptor import TensorDescriptor
+
+pytestmark = pytest.mark.gpu
+
+MATMUL_REL_FRO = 1e-2
+ATTN_MAX_ABS = 2e-2
+SIN_MAX_ULP = 2
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    if not torch.cuda.is_available():
+        pytest.fail("the -m gpu tests need a CUDA device")
+    torch.cuda.set_device(0)
+    yield
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0, "a kernel reported a bounded-wait timeout"
+
+
+def _bf16(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def _bits_equal(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return torch.equal(a.contiguous().view(torch.int32), b.contiguous().view(torch.int32))
+
+
+# ------------------------------------------------------------------------------------------------ add
+@pytest.mark.parametrize("n", gi.ADD_SIZES)
+def test_add_golden_bit_exact(golden_dir, n):
+    g = np.load(golden_dir / "add.npz")
+    x, y = gi.add_inputs(n)
+    out = ops.add(x.cuda(), y.cuda()).cpu()
+    assert np.array_equal(out.numpy().view(np.uint32), g[f"out_{n}"].view(np.uint32))
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 1023, 1025, 4099, 66560, (1 << 20) + 7])
+def test_add_oracle_bit_exact_edges(n):
+    x, y = gi.add_inputs(n, seed=3)
+    got = ops.add(x.cuda(), y.cuda()).cpu()
+    assert _bits_equal(got, oracle.add(x, y)) if n else got.numel() == 0
+
+
+def test_add_unaligned_views_and_canaries():
+    x, y = gi.add_inputs(5003, seed=5)
+    xd, yd = x.cuda(), y.cuda()
+    for off in (1, 2, 3):
+        got = ops.add(xd[off:], yd[off:]).cpu()           # 4-byte aligned only: scalar path
+        assert _bits_equal(got, oracle.add(x[off:], y[off:]))
+    # direct C-ABI call into the middle of a canary-filled buffer: nothing outside [0, n) is written
+    n = 4097
+    buf = torch.full((n + 64,), -7.0, device="cuda")
+    lib = _lib.load()
+    _lib.check(lib.b200k_add_f32(xd.data_ptr(), yd.data_ptr(), buf[32:].data_ptr(), n, 1024,
+                                 torch.cuda.current_stream().cuda_stream))
+    host = buf.cpu()
+    assert torch.all(host[:32] == -7.0) and torch.all(host[32 + n:] == -7.0)
+    assert _bits_equal(host[32:32 + n], oracle.add(x[:n], y[:n]))
+
+
+def test_add_full_size_property():
+    # 2^26 elements: the same bits as an fp32 add done by torch on the device
+    n = 1 << 26
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x, y = torch.rand(n, device="cuda", generator=g), torch.rand(n, device="cuda", generator=g)
+    assert torch.equal(ops.add(x, y), x + y)
+
+
+def test_mul_add_oracle_bit_exact():
+    x, y = gi.add_inputs(98432, seed=7)
+    z = gi.sin_inputs(98432, seed=8)
+    got = ops.mul_add(x.cuda(), y.cuda(), z.cuda()).cpu()
+    assert _bits_equal(got, oracle.mul_add(x, y, z))
+
+
+# ------------------------------------------------------------------------------------------------ sin
+@pytest.mark.parametrize("n", gi.SIN_SIZES)
+def test_sin_golden_within_2ulp(golden_dir, n):
+    g = np.load(golden_dir / "sin.npz")
+    x = gi.sin_inputs(n)
+    got = ops.sin(x.cuda()).cpu()
+    assert oracle.ulp_diff_f32(got, torch.from_numpy(g[f"out_{n}"])) <= SIN_MAX_ULP
+    assert oracle.ulp_diff_f32(got, oracle.sin(x)) <= SIN_MAX_ULP            # the CPU path's libm sinf
+    assert oracle.ulp_diff_f32(got, oracle.sin_correctly_rounded(x)) <= SIN_MAX_ULP
+
+
+def test_sin_full_size_within_2ulp():
+    n = 1 << 26
+    x = gi.sin_inputs(n, seed=11)
+    got = ops.sin(x.cuda()).cpu()
+    assert oracle.ulp_diff_f32(got, oracle.sin_correctly_rounded(x)) <= SIN_MAX_ULP
+    assert oracle.pcc(got[: 1 << 20], oracle.sin_correctly_rounded(x[: 1 << 20])) > 0.97   # the reference's own gate
+
+
+def test_sin_ragged_and_special_values():
+    x = torch.tensor([0.0, -0.0, math.pi, -math.pi, 4 * math.pi, -4 * math.pi, 1e-30, 0.5, 100.0, -1234.5, 1e6],
+                     dtype=torch.float32)
+    got = ops.sin(x.cuda()).cpu()
+    ref = oracle.sin_correctly_rounded(x)
+    assert oracle.ulp_diff_f32(got, ref) <= SIN_MAX_ULP
+    assert math.copysign(1.0, got[1].item()) == -1.0    # sin(-0) = -0
+
+
+# ------------------------------------------------------------------------------------------------ matmul
+@pytest.mark.parametrize("shape", gi.MATMUL_SHAPES)
+def test_matmul_golden(golden_dir, shape):
+    M, N, K = shape
+    g = np.load(golden_dir / "matmul.npz")
+    a, b = gi.matmul_inputs(M, N, K)
+    golden = _bf16(g[f"c_{M}x{N}x{K}"])
+    got = ops.matmul_tma(a.cuda(), b.cuda(), warp_specialize=True).cpu()
+    assert oracle.rel_frobenius(got.float(), golden.float()) <= MATMUL_REL_FRO
+    # in fact only summation order differs: at most one bf16 ulp, rarely
+    assert float((got.float() - golden.float()).abs().max()) <= float(golden.float().abs().max()) * 2 ** -7
+    assert float((got.view(torch.int16) != golden.view(torch.int16)).float().mean()) < 5e-3
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (512, 384, 640), (200, 264, 136), (1000, 8, 72), (40, 1032, 8),
+                                   (1024, 1024, 1024), (129, 257 * 8, 65 * 8)])
+def test_matmul_oracle_shapes_and_tails(shape):
+    M, N, K = shape
+    a, b = gi.matmul_inputs(M, N, K, seed=2)
+    ref = oracle.golden_matmul(a, b)
+    c = torch.full((M, N), 7.5, dtype=torch.bfloat16, device="cuda")   # the reference pre-fills C with 7.5
+    got = ops._matmul_call(a.cuda(), b.cuda(), c=c).cpu()
+    assert not torch.any(got == 7.5), "an element of C was left unwritten"
+    assert oracle.rel_frobenius(got.float(), ref.float()) <= MATMUL_REL_FRO
+    assert oracle.pcc(got.float(), ref.float()) > 0.97
+
+
+def test_matmul_strided_operands_and_canaries():
+    M, N, K = 300, 200, 264
+    a, b = gi.matmul_inputs(M, N, K, seed=4)
+    abig = torch.zeros(M, K + 24, dtype=torch.bfloat16, device="cuda"); abig[:, :K] = a.cuda()
+    bbig = torch.zeros(K, N + 8, dtype=torch.bfloat16, device="cuda"); bbig[:, :N] = b.cuda()
+    cbig = torch.full((M + 2, N + 16), -3.0, dtype=torch.bfloat16, device="cuda")
+    ops._matmul_call(abig[:, :K], bbig[:, :N], c=cbig[:M, :N])
+    host = cbig.cpu()
+    assert torch.all(host[M:, :] == -3.0) and torch.all(host[:, N:] == -3.0), "store outside [M,N]"
+    ref = oracle.golden_matmul(a, b)
+    assert oracle.rel_frobenius(host[:M, :N].float(), ref.float()) <= MATMUL_REL_FRO
+
+
+def test_matmul_activation_and_bias_epilogues():
+    M, N, K = 384, 320, 256
+    a, b, bias_full = gi.fused_inputs(M, N, K, seed=6)
+    bias_row = gi.row_bias(N)
+    ad, bd = a.cuda(), b.cuda()
+    cases = [
+        (ops.matmul(ad, bd, activation="leaky_relu"), oracle.golden_matmul(a, b, mode=0, activation="leaky_relu")),
+        (ops.matmul(ad, bd, activation="relu"), oracle.golden_matmul(a, b, mode=0, activation="relu")),
+        (ops.matmul_fused(ad, bd, bias_row.cuda(), activation="relu"),
+         oracle.golden_matmul(a, b, bias=bias_row, mode=3, activation="relu")),
+        (ops.matmul_fused(ad, bd, bias_row.cuda(), activation=""), oracle.golden_matmul(a, b, bias=bias_row, mode=3)),
+        (ops.matmul_tma_fused(ad, bd, bias_full.cuda(), True), oracle.golden_matmul(a, b, bias=bias_full, mode=2)),
+        (ops.matmul_tma_fused(ad, bd, bias_full.cuda(), True, round_before_bias=False),
+         oracle.golden_matmul(a, b, bias=bias_full, mode=1)),
+    ]
+    for got, ref in cases:
+        got = got.cpu()
+        assert oracle.rel_frobenius(got.float(), ref.float()) <= MATMUL_REL_FRO
+        assert float((got.view(torch.int16) != ref.view(torch.int16)).float().mean()) < 1e-2
+    relu = cases[2][0].cpu().float()
+    assert float(relu.min()) >= 0.0 and float((relu == 0).float().mean()) > 0.2
+
+
+def test_matmul_fused_tail_bias():
+    # N not a multiple of 64 and M not a multiple of 32: the guarded bias paths
+    M, N, K = 100, 72, 64
+    a, b, bias_full = gi.fused_inputs(M, N, K, seed=9)
+    bias_row = gi.row_bias(N)
+    got = ops.matmul_fused(a.cuda(), b.cuda(), bias_row.cuda()).cpu()
+    assert oracle.rel_frobenius(got.float(), oracle.golden_matmul(a, b, bias=bias_row, mode=3, activation="relu").float()) <= MATMUL_REL_FRO
+    got = ops.matmul_tma_fused(a.cuda(), b.cuda(), bias_full.cuda()).cpu()
+    assert oracle.rel_frobenius(got.float(), oracle.golden_matmul(a, b, bias=bias_full, mode=2).float()) <= MATMUL_REL_FRO
+
+
+@pytest.mark.parametrize("S", [4096, 8192])
+def test_matmul_full_size_rows_against_oracle(S):
+    # full-size problem on the GPU; the oracle recomputes a sample of rows (whole rows of C, all of B)
+    a, b = gi.matmul_inputs(S, S, S, seed=12)
+    got = ops.matmul_tma(a.cuda(), b.cuda())
+    rows = torch.tensor([0, 1, 127, 128, S // 2 + 3, S - 129, S - 1] + list(range(1000, 1000 + 25)))
+    ref = oracle.golden_matmul(a[rows], b)
+    assert oracle.rel_frobenius(got[rows.cuda()].cpu().float(), ref.float()) <= MATMUL_REL_FRO
+    # linearity in A: (2A).B == 2 (A.B) exactly (power-of-two scaling commutes with every rounding)
+    got2 = ops.matmul_tma((a * 2).cuda(), b.cuda())
+    assert torch.equal(got2, got * 2)
+
+
+def test_matmul_fused_workload_shape_sample():
+    M, N, K = 16384, 4096, 4096
+    a, b = gi.matmul_inputs(M, N, K, seed=13)
+    bias = gi.row_bias(N)
+    got = ops.matmul_fused(a.cuda(), b.cuda(), bias.cuda(), activation="relu")
+    rows = torch.arange(0, M, 512)
+    ref = oracle.golden_matmul(a[rows], b, bias=bias, mode=3, activation="relu")
+    assert oracle.rel_frobenius(got[rows.cuda()].cpu().float(), ref.float()) <= MATMUL_REL_FRO
+
+
+def test_matmul_rejects_bad_arguments():
+    a = torch.zeros(64, 36, dtype=torch.bfloat16, device="cuda")      # 72-byte rows
+    b = torch.zeros(36, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        ops.matmul_tma(a, b)
+    with pytest.raises(AssertionError):
+        ops.matmul_tma(torch.zeros(64, 32, dtype=torch.bfloat16, device="cuda"), b)   # K mismatch
+    lib = _lib.load()
+    t = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    rc = lib.b200k_matmul_bf16(t.data_ptr() + 2, t.data_ptr(), t.data_ptr(), 32, 32, 32, 64, 64, 64, None, 0, 0, 0, 0, None)
+    assert rc == _lib.ERR_INVALID_ARG and "16-byte aligned" in _lib.last_error()
+
+
+# ------------------------------------------------------------------------------------------------ attention
+@pytest.mark.parametrize("case", [c for c in gi.ATTN_CASES if c[3] == 128])
+def test_attention_golden(golden_dir, case):
+    Z, H, S, D, causal, BM, BN = case
+    g = np.load(golden_dir / "attention.npz")
+    q, k, v = gi.attn_inputs(Z, H, S, D)
+    tag = f"{Z}x{H}x{S}x{D}_{'c' if causal else 'n'}_{BM}x{BN}"
+    golden_o, golden_m = _bf16(g[f"o_{tag}"]), torch.from_numpy(g[f"M_{tag}"])
+    o, m = ops.attention_with_lse(q.cuda(), k.cuda(), v.cuda(), causal, D ** -0.5)
+    assert float((o.cpu().float() - golden_o.float()).abs().max()) <= ATTN_MAX_ABS
+    assert float((m.cpu() - golden_m).abs().max()) <= 1e-4
+
+
+@pytest.mark.parametrize("Z,H,S,causal", [(1, 1, 128, False), (1, 1, 128, True), (1, 3, 384, True), (2, 2, 512, False),
+                                          (1, 2, 1024, True), (1, 1, 2048, False), (3, 5, 256, True)])
+def test_attention_oracle(Z, H, S, causal):
+    D = 128
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=21)
+    ref_o, ref_m = oracle.attention(q, k, v, causal, D ** -0.5, BLOCK_M=128, BLOCK_N=128)
+    o, m = ops.attention_with_lse(q.cuda(), k.cuda(), v.cuda(), causal, D ** -0.5)
+    assert float((o.cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
+    assert float((m.cpu() - ref_m).abs().max()) <= 1e-4
+    assert oracle.pcc(o.cpu().float(), ref_o.float()) > 0.999
+
+
+def test_attention_scale_and_large_logits():
+    # large sm_scale: sharp softmax, exercises the running-maximum updates and the rescale of O
+    Z, H, S, D = 1, 2, 512, 128
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=22)
+    for causal in (False, True):
+        ref_o, ref_m = oracle.attention(q, k, v, causal, 0.5)
+        o, m = ops.attention_with_lse(q.cuda(), k.cuda(), v.cuda(), causal, 0.5)
+        assert float((o.cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
+        assert float((m.cpu() - ref_m).abs().max()) <= 1e-3
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_full_size_heads_against_oracle(causal):
+    # the full workload on the GPU; the oracle recomputes two (batch, head) pairs
+    Z, H, S, D = 4, 32, 4096, 128
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=23)
+    o, m = ops.attention_with_lse(q.cuda(), k.cuda(), v.cuda(), causal, D ** -0.5)
+    for (z, h) in ((0, 0), (3, 31)):
+        sl = (slice(z, z + 1), slice(h, h + 1))
+        ref_o, ref_m = oracle.attention(q[sl], k[sl], v[sl], causal, D ** -0.5)
+        assert float((o[sl].cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
+        assert float((m[sl].cpu() - ref_m).abs().max()) <= 1e-4
+    # rows of softmax sum to one: with V = 1 the output is exactly 1 (l normalisation)
+    ones = torch.ones_like(v[:1, :2]).cuda()
+    o1 = ops.attention(q[:1, :2].cuda(), k[:1, :2].cuda(), ones, causal, D ** -0.5)
+    assert float((o1.float() - 1).abs().max()) <= 2 ** -7
+
+
+def test_attention_rejects_unsupported():
+    q = torch.zeros(1, 1, 100, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NotImplementedError):
+        ops.attention(q, q, q, False, 0.1)
+    q64 = torch.zeros(1, 1, 128, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NotImplementedError):
+        ops.attention(q64, q64, q64, False, 0.1)
+
+
+# ------------------------------------------------------------------------------------------------ launch surface
+def test_kernel_grid_launch_surface():
+    n = 98432
+    x, y = gi.add_inputs(n)
+    xd, yd = x.cuda(), y.cuda()
+    out = torch.empty_like(xd)
+    grid = lambda meta: ((n + meta["BLOCK_SIZE"] - 1) // meta["BLOCK_SIZE"],)
+    kernels.add_kernel[grid](xd, yd, out, n, BLOCK_SIZE=1024)
+    assert _bits_equal(out.cpu(), oracle.add(x, y))
+    kernels.sin_kernel[grid](xd, out, n, BLOCK_SIZE=1024)
+    assert oracle.ulp_diff_f32(out.cpu(), oracle.sin_correctly_rounded(x)) <= SIN_MAX_ULP
+
+    M, N, K = 256, 512, 192
+    a, b, bias = gi.fused_inputs(M, N, K, seed=31)
+    ad, bd, biasd = a.cuda(), b.cuda(), bias.cuda()
+    c = torch.full((M, N), 7.5, device="cuda", dtype=torch.bfloat16)
+    descs = [TensorDescriptor.from_tensor(t, [32, 32]) for t in (ad, bd, c)]
+    mgrid = lambda META: (-(-M // META["BLOCK_SIZE_M"]) * -(-N // META["BLOCK_SIZE_N"]),)
+    kernels.matmul_kernel_tma[mgrid](*descs, M, N, K, FP8_OUTPUT=False, WARP_SPECIALIZE=True)
+    assert oracle.rel_frobenius(c.cpu().float(), oracle.golden_matmul(a, b).float()) <= MATMUL_REL_FRO
+    kernels.matmul_kernel_fused[mgrid](*descs, TensorDescriptor.from_tensor(biasd, [32, 32]), M, N, K,
+                                       FP8_OUTPUT=False, WARP_SPECIALIZE=True)
+    assert oracle.rel_frobenius(c.cpu().float(), oracle.golden_matmul(a, b, bias=bias, mode=2).float()) <= MATMUL_REL_FRO
+
+    Z, H, S, D = 1, 2, 256, 128
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=32)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o = torch.empty_like(qd)
+    Mt = torch.empty((Z, H, S), device="cuda", dtype=torch.float32)
+    ydim = Z * H * S
+    dq, dk, dv, do = (TensorDescriptor(t, shape=[ydim, D], strides=[D, 1], block_shape=[1, 1]) for t in (qd, kd, vd, o))
+    agrid = lambda META: (-(-S // META["BLOCK_M"]), Z * H, 1)
+    kernels._attn_fwd[agrid](D ** -0.5, Mt, Z, H, dq, dk, dv, do, N_CTX=S, HEAD_DIM=D, FP8_OUTPUT=False, STAGE=3,
+                             warp_specialize=True, IS_HOPPER=False)
+    ref_o, ref_m = oracle.attention(q, k, v, True, D ** -0.5)
+    assert float((o.cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
+    assert float((Mt.cpu() - ref_m).abs().max()) <= 1e-4
+
+
+def test_host_tensor_round_trip():
+    # host buffers in, host result out: what the reference's launcher does on every launch
+    x, y = gi.add_inputs(98432)
+    out = ops.add(x, y)
+    assert not out.is_cuda and _bits_equal(out, oracle.add(x, y))
+    a, b = gi.matmul_inputs(256, 256, 256)
+    c = ops.matmul_tma(a, b, True)
+    assert not c.is_cuda and oracle.rel_frobenius(c.float(), oracle.golden_matmul(a, b).float()) <= MATMUL_REL_FRO
+
+
+def test_launch_counter_counts_kernels():
+    lib = _lib.load()
+    before = lib.b200k_launch_count()
+    x = torch.zeros(4096, device="cuda")
+    ops.add(x, x)
+    assert lib.b200k_launch_count() == before + 1
+    props = _lib.Props()
+    _lib.check(lib.b200k_device_props(0, ctypes.byref(props)))
+    assert props.cc_major == 10 and props.multiprocessor_count >= 100

@@ -1,0 +1,145 @@
+"""Host-side mirror of the reference interface: argument flattening, kernel[grid] binding,
+descriptors, partition helpers.  No GPU needed (a recording launcher stands in for the C-ABI call)."""
+import pytest
+import torch
+
+from oracle import cpu_oracle as oracle
+from triton_tenstorrent_b200 import _lib, driver, kernels, sharding
+from triton_tenstorrent_b200.tensor_descriptor import TensorDescriptor
+
+
+class FakeCudaTensor(torch.Tensor):
+    """A host tensor that claims to be on the GPU, to drive the launch surface without one."""
+    @property
+    def is_cuda(self):
+        return True
+
+
+def fake(t):
+    return t.as_subclass(FakeCudaTensor)
+
+
+class RecordingLauncher:
+    calls = []
+
+    def __init__(self, src, metadata):
+        self.signature = dict(src.signature)
+
+    def __call__(self, gx, gy, gz, stream, function, *args):
+        RecordingLauncher.calls.append(dict(grid=(gx, gy, gz), function=function, metadata=args[0],
+                                            flat=driver.flatten_args(self.signature, args[4:])))
+
+
+@pytest.fixture
+def recording(monkeypatch):
+    RecordingLauncher.calls = []
+    monkeypatch.setattr(driver.active, "launcher_cls", RecordingLauncher)
+    monkeypatch.setattr(driver.active, "get_current_stream", lambda device_id=None: 0)
+    for k in (kernels.add_kernel, kernels.sin_kernel, kernels.matmul_kernel_tma, kernels.matmul_kernel_fused, kernels._attn_fwd):
+        monkeypatch.setattr(k, "launcher", None)
+    return RecordingLauncher.calls
+
+
+def test_add_kernel_launch_surface(recording):
+    n = 98432
+    x, y, out = (fake(torch.zeros(n)) for _ in range(3))
+    grid = lambda meta: ((n + meta["BLOCK_SIZE"] - 1) // meta["BLOCK_SIZE"],)
+    kernels.add_kernel[grid](x, y, out, n, BLOCK_SIZE=1024)
+    call = recording[0]
+    assert call["grid"] == (97, 1, 1)                      # 98432 = 96*1024 + 128
+    assert call["function"] == "add_kernel:BLOCK_SIZE=1024"
+    assert call["metadata"] == (1, 1, 0, 1, 1, 1)          # num_warps, num_ctas, shared, cluster dims
+    kinds = [k for k, _ in call["flat"]]
+    assert kinds == [_lib.ARG_PTR] * 3 + [_lib.ARG_I32]    # the constexpr BLOCK_SIZE is dropped
+    assert call["flat"][3][1] == n
+    assert [v for _, v in call["flat"][:3]] == [x.data_ptr(), y.data_ptr(), out.data_ptr()]
+
+
+def test_descriptor_flattening_matches_reference_order(recording):
+    M, N, K = 256, 512, 128
+    a, b, c = fake(torch.zeros(M, K, dtype=torch.bfloat16)), fake(torch.zeros(K, N, dtype=torch.bfloat16)), fake(torch.zeros(M, N, dtype=torch.bfloat16))
+    descs = [TensorDescriptor.from_tensor(t, [32, 32]) for t in (a, b, c)]
+    grid = lambda META: (-(-M // META["BLOCK_SIZE_M"]) * -(-N // META["BLOCK_SIZE_N"]),)
+    kernels.matmul_kernel_tma[grid](*descs, M, N, K, FP8_OUTPUT=False, WARP_SPECIALIZE=True)
+    call = recording[0]
+    assert call["grid"] == (2 * 2, 1, 1)
+    flat = call["flat"]
+    assert len(flat) == 3 * 10 + 3
+    # base, shape.., strides.., padding, shape.., strides..   (backend/driver.py:141-159)
+    first = [v for _, v in flat[:10]]
+    assert first == [a.data_ptr(), M, K, K, 1, 0, M, K, K, 1]
+    assert [v for _, v in flat[-3:]] == [M, N, K]
+
+
+def test_attention_launch_surface(recording):
+    Z, H, S, D = 2, 3, 256, 128
+    q = fake(torch.zeros(Z, H, S, D, dtype=torch.bfloat16))
+    Mt = fake(torch.zeros(Z, H, S))
+    y = Z * H * S
+    d = [TensorDescriptor(q, shape=[y, D], strides=[D, 1], block_shape=[1, 1]) for _ in range(4)]
+    grid = lambda META: (-(-S // META["BLOCK_M"]), Z * H, 1)
+    kernels._attn_fwd[grid](0.5, Mt, Z, H, *d, N_CTX=S, HEAD_DIM=D, FP8_OUTPUT=False, STAGE=3, warp_specialize=True,
+                            IS_HOPPER=False)
+    call = recording[0]
+    assert call["grid"] == (2, 6, 1)
+    assert call["function"] == "_attn_fwd:STAGE=3"
+    kinds = [k for k, _ in call["flat"]]
+    assert kinds[0] == _lib.ARG_F32 and kinds[1] == _lib.ARG_PTR and len(kinds) == 4 + 40 + 1
+    assert call["flat"][-1][1] == S
+
+
+def test_kernel_argument_errors(recording):
+    x = fake(torch.zeros(8))
+    with pytest.raises(TypeError):
+        kernels.add_kernel[(1,)](x, x, x, 8)                       # BLOCK_SIZE missing
+    with pytest.raises(TypeError):
+        kernels.add_kernel[(1,)](x, x, x, 8, BLOCK_SIZE=8, bogus=1)
+    with pytest.raises(ValueError):
+        kernels.add_kernel[(1,)](torch.zeros(8), x, x, 8, BLOCK_SIZE=8)  # host tensor
+    kernels.add_kernel[(1,)](x, x, x, 8, BLOCK_SIZE=8, num_warps=4, num_stages=2)  # accepted and ignored
+    assert len(recording) == 1
+
+
+def test_tensor_descriptor_checks():
+    t = torch.zeros(64, 24, dtype=torch.bfloat16)
+    d = TensorDescriptor.from_tensor(t, [32, 32])
+    assert d.shape == [64, 24] and d.strides == [24, 1] and d.padding == "zero"
+    with pytest.raises(AssertionError):
+        TensorDescriptor.from_tensor(torch.zeros(64, 20, dtype=torch.bfloat16), [32, 32])  # 40-byte rows
+    with pytest.raises(AssertionError):
+        TensorDescriptor(t, [64, 24], [1, 64], [32, 32])                                    # inner stride != 1
+
+
+def test_load_binary_and_target():
+    u = driver.B200Utils()
+    mod, fn, n_regs, n_spills, max_threads = u.load_binary("matmul_kernel_tma", b"", 0, 0)
+    assert fn == "matmul_kernel_tma"
+    with pytest.raises(KeyError):
+        u.load_binary("not_a_kernel", b"", 0, 0)
+    assert driver.active.get_current_target() == ("cuda", 100, 32)
+    assert driver.pack_metadata(4, 1, 1024) == (4, 1, 1024, 1, 1, 1)
+
+
+@pytest.mark.parametrize("nb,workers", [(97, 8), (5, 8), (2048, 148), (0, 3), (16, 16)])
+def test_block_range_matches_oracle_and_covers(nb, workers):
+    covered = []
+    for w in range(workers):
+        r = sharding.block_range(nb, workers, w)
+        assert r == oracle.block_range(nb, workers, w)
+        covered.extend(range(*r))
+    assert covered == list(range(nb))
+
+
+def test_row_and_head_shards():
+    assert [sharding.row_shard(8192, 8, r) for r in range(8)] == [(1024 * r, 1024 * (r + 1)) for r in range(8)]
+    spans = [sharding.row_shard(1000, 3, r) for r in range(3)]      # 8 tiles of 128 rows -> 3,3,2 tiles
+    assert spans == [(0, 384), (384, 768), (768, 1000)]
+    assert [sharding.head_shard(128, 8, r) for r in (0, 7)] == [(0, 16), (112, 128)]
+
+
+def test_ops_fail_loudly_without_cuda():
+    from triton_tenstorrent_b200 import ops
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(Exception):
+        ops.add(torch.zeros(8), torch.zeros(8))

@@ -32,8 +32,18 @@ def _to_device(t: torch.Tensor) -> torch.Tensor:
     return t.to("cuda", non_blocking=True)
 
 
-def _like_input(result: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
-    """Returns `result` on the device `ref` lives on (host inputs get a host result)."""
+def _like_input(result: torch.Tensor, ref: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """Returns `result` on the device `ref` lives on (host inputs get a host result).  With `out`
+    (an extension over the reference wrappers) the result is copied into that tensor instead, e.g. a
+    pinned host buffer the caller reuses between calls; the copy is complete on return."""
+    if out is not None:
+        if out.shape != result.shape or out.dtype != result.dtype:
+            raise ValueError(f"out must be {tuple(result.shape)} {result.dtype}")
+        if out.data_ptr() != result.data_ptr():
+            out.copy_(result, non_blocking=True)
+            if not out.is_cuda:
+                torch.cuda.current_stream().synchronize()
+        return out
     if ref.is_cuda:
         return result
     return result.to("cpu")
@@ -113,6 +123,10 @@ def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT
         raise ValueError(f"matmul: N must be a multiple of 8 (16-byte rows of C); got {N}")
     if c is None:
         c = torch.empty((M, N), device=ad.device, dtype=torch.bfloat16)
+    elif (tuple(c.shape) != (M, N) or c.dtype != torch.bfloat16 or not c.is_cuda or c.device != ad.device
+          or c.stride(1) != 1 or c.stride(0) % 8 != 0 or c.data_ptr() % 16 != 0):
+        raise ValueError(f"matmul: the output must be a bf16 [{M},{N}] tensor on {ad.device} with unit inner stride "
+                         "and 16-byte aligned rows")
     bias_ptr, ldbias = 0, 0
     if bias_kind == _lib.BIAS_ROW_F32:
         bias = _to_device(bias).contiguous()
@@ -133,11 +147,11 @@ def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT
     return c
 
 
-def matmul_tma(a: torch.Tensor, b: torch.Tensor, warp_specialize: bool = True) -> torch.Tensor:
+def matmul_tma(a: torch.Tensor, b: torch.Tensor, warp_specialize: bool = True, out: torch.Tensor = None) -> torch.Tensor:
     """C = A.B, bf16 in/out, fp32 accumulate.  Mirrors matmul_tma(a, b, warp_specialize),
     examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py:146-173.  `warp_specialize` is accepted for
     surface compatibility; the kernel is always warp-specialised."""
-    return _like_input(_matmul_call(a, b), a)
+    return _like_input(_matmul_call(a, b, c=out if (out is not None and out.is_cuda) else None), a, out)
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "") -> torch.Tensor:
@@ -150,12 +164,14 @@ def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "") -> torch.Tens
     return _like_input(_matmul_call(a, b, act=_ACTIVATIONS[activation]), a)
 
 
-def matmul_fused(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor, activation: str = "relu") -> torch.Tensor:
+def matmul_fused(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor, activation: str = "relu",
+                 out: torch.Tensor = None) -> torch.Tensor:
     """C = act(A.B + bias[N]) in one kernel: fp32 bias add and activation on the accumulator, one downcast.
     This is the [N]-bias + ReLU epilogue of the fused-matmul workload."""
     if activation not in _ACTIVATIONS:
         raise ValueError(f"unknown activation {activation!r}")
-    return _like_input(_matmul_call(a, b, bias=bias, bias_kind=_lib.BIAS_ROW_F32, act=_ACTIVATIONS[activation]), a)
+    return _like_input(_matmul_call(a, b, c=out if (out is not None and out.is_cuda) else None, bias=bias,
+                                    bias_kind=_lib.BIAS_ROW_F32, act=_ACTIVATIONS[activation]), a, out)
 
 
 def matmul_tma_fused(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor, warp_specialize: bool = True,
