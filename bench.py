@@ -66,7 +66,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -191,11 +191,15 @@ def quick_ms(fn, torch, warm=3, rep=10):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-workload", default=None,
+                    choices=["matmul", "matmul_fused", "add", "sin", "attention", "attention_causal"],
+                    help="launch only this kernel warmup+steps times and print nothing to time: the small, "
+                         "bounded command the ncu captures summarised under profiles/ are taken from")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -221,6 +225,9 @@ def main():
         dist = dist_mod
     lib = _lib.load()
     peaks = measured_peaks()
+    if args.profile_workload:
+        profile_workload(args, torch, ops, gi)
+        return
 
     # ---- inputs: every rank owns one 8192-row block of A and C, and a replica of B
     a_host = gi.matmul_inputs(M, N, K, seed=100 + rank)[0]
@@ -235,16 +242,16 @@ def main():
     launches0 = lib.b200k_launch_count()
     with ClockSampler(local_rank) as clocks:
         ms = time_region(step, args.steps, dist, torch)
-    launches = lib.b200k_launch_count() - launches0
+        launches = lib.b200k_launch_count() - launches0
+        # ---- kernel-only duration for the roofline: the step IS one kernel launch; per-launch events
+        #      (same launches back to back, so the clock samples cover both loops)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        torch.cuda.synchronize()
+        for s, e in evs:
+            s.record(); step(); e.record()
+        torch.cuda.synchronize()
     ops.device_status()
     value = world * FLOP_PER_STEP / (ms * 1e-3) / 1e12
-
-    # ---- kernel-only duration for the roofline: the step IS one kernel launch; per-launch events
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    torch.cuda.synchronize()
-    for s, e in evs:
-        s.record(); step(); e.record()
-    torch.cuda.synchronize()
     kernel_ms = statistics.fmean(s.elapsed_time(e) for s, e in evs)
     achieved = FLOP_PER_STEP / (kernel_ms * 1e-3) / 1e12
     sustained = args.steps * ms > 1000.0     # a second or more of back-to-back launches
@@ -298,6 +305,36 @@ def main():
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def profile_workload(args, torch, ops, gi):
+    """One kernel, warmup + steps launches, workload-sized inputs (all larger than L2, under 1 GB)."""
+    w = args.profile_workload
+    if w == "matmul":
+        a = (torch.randn(M, K, device="cuda") / K ** 0.5).bfloat16()
+        b = (torch.randn(K, N, device="cuda") / K ** 0.5).bfloat16()
+        c = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+        fn = lambda: ops.matmul_tma(a, b, True, out=c)
+    elif w == "matmul_fused":
+        a = (torch.randn(16384, 4096, device="cuda") / 64).bfloat16()
+        b = (torch.randn(4096, 4096, device="cuda") / 64).bfloat16()
+        bias = torch.randn(4096, device="cuda") * 0.1
+        c = torch.empty((16384, 4096), device="cuda", dtype=torch.bfloat16)
+        fn = lambda: ops.matmul_fused(a, b, bias, "relu", out=c)
+    elif w in ("add", "sin"):
+        n = 1 << 26
+        x, y = torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
+        fn = (lambda: ops.add(x, y)) if w == "add" else (lambda: ops.sin(x))
+    else:
+        q = torch.randn(4, 32, 4096, 128, device="cuda").bfloat16()
+        k, v = torch.randn_like(q), torch.randn_like(q)
+        causal = w == "attention_causal"
+        fn = lambda: ops.attention(q, k, v, causal, 128 ** -0.5)
+    for _ in range(args.warmup + args.steps):
+        fn()
+    torch.cuda.synchronize()
+    ops.device_status()
+    print(json.dumps({"profile_workload": w, "launches": args.warmup + args.steps}), flush=True)
 
 
 def secondary_workloads(torch, ops, gi, peaks, dist, world, rank, a, b, c, sharding):
