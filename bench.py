@@ -38,8 +38,8 @@ FLOP_PER_STEP = 2.0 * M * N * K
 METRIC = "bf16 matmul TFLOP/s (persistent tensor-descriptor matmul, M=N=K=8192 per GPU)"
 
 # DRAM traffic of one 8192^3 launch of matmul_bf16_tcgen05_kernel<256,4> from an ncu capture
-# (dram__bytes_read.sum + dram__bytes_write.sum; profiles/matmul_bf16_8192.md); None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# (dram__bytes_read.sum 1.406 GB + dram__bytes_write.sum 127.4 MB; profiles/matmul_bf16_tcgen05_8192.md).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1_533_478_000
 
 
 def measured_peaks():
