@@ -443,7 +443,8 @@ static int pick_grid(int sm_count, int num_items, int num_pairs, bool causal) {
   return grid;
 }
 
-int attn_fwd_bf16(const AttnArgs& a, cudaStream_t stream) {
+// Argument checks shared by the entry points.
+static int attn_check_args(const AttnArgs& a) {
   if (a.Z <= 0 || a.H <= 0 || a.N_CTX <= 0) return set_error(B200K_ERR_INVALID_ARG, "attention: Z, H, N_CTX must be positive");
   if (!attn_supported(a.D, a.N_CTX))
     return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 128, N_CTX multiple of 128)", a.D, a.N_CTX);
@@ -455,10 +456,12 @@ int attn_fwd_bf16(const AttnArgs& a, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
   if (rows > 0x7FFFFFFF) return set_error(B200K_ERR_INVALID_ARG, "attention: Z*H*N_CTX exceeds 2^31-1 rows");
   if (!(a.sm_scale > 0.f) || !isfinite(a.sm_scale)) return set_error(B200K_ERR_INVALID_ARG, "attention: sm_scale must be positive and finite");
-  const DeviceInfo* dev = current_device_info();
-  if (dev == nullptr) return B200K_ERR_NO_DEVICE;
-  if (dev->cc_major != 10) return set_error(B200K_ERR_NO_DEVICE, "attention: needs an sm_100 device (found sm_%d%d)", dev->cc_major, dev->cc_minor);
+  return B200K_OK;
+}
 
+// Encodes the tensor maps and launches the kernel on `sm_count` SMs, reporting to `status`.
+static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uint32_t* status) {
+  const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
   CUtensorMap tq, tk, tv, to;
   int rc;
   if ((rc = make_tmap_bf16_2d(&tq, a.q, AT_D, rows, AT_D, 64, AT_BM)) != 0) return rc;
@@ -475,20 +478,26 @@ int attn_fwd_bf16(const AttnArgs& a, cudaStream_t stream) {
   p.causal = a.causal ? 1 : 0;
   p.qk_scale = a.sm_scale * 1.44269504f;
   p.lse2 = a.lse2;
-  p.status = dev->status_word;
+  p.status = status;
 
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          AT_SMEM_TOTAL));
-    attr_set = true;
-  }
-  int grid = pick_grid(dev->sm_count, p.num_items, p.num_pairs, p.causal != 0);
+  // per device (function attributes belong to the current context), cheap enough to repeat
+  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        AT_SMEM_TOTAL));
+  int grid = pick_grid(sm_count, p.num_items, p.num_pairs, p.causal != 0);
   if (const char* g = getenv("B200K_ATTN_GRID")) { int v = atoi(g); if (v > 0 && v <= p.num_items) grid = v; }
   attn_fwd_bf16_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_TOTAL, stream>>>(tq, tk, tv, to, p);
   count_launch();
   B200K_CHECK_LAUNCH("attn_fwd_bf16_tcgen05_kernel");
   return B200K_OK;
+}
+
+int attn_fwd_bf16(const AttnArgs& a, cudaStream_t stream) {
+  const int rc = attn_check_args(a);
+  if (rc != B200K_OK) return rc;
+  const DeviceInfo* dev = current_device_info();
+  if (dev == nullptr) return B200K_ERR_NO_DEVICE;
+  if (dev->cc_major != 10) return set_error(B200K_ERR_NO_DEVICE, "attention: needs an sm_100 device (found sm_%d%d)", dev->cc_major, dev->cc_minor);
+  return attn_launch(a, stream, dev->sm_count, dev->status_word);
 }
 
 }  // namespace b200k

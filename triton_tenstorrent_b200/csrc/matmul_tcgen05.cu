@@ -347,12 +347,9 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   }
   p.status = status;
 
-  static bool attr_set = false;  // per instantiation; benign race (idempotent call)
-  if (!attr_set) {
-    B200K_CHECK_CUDA(cudaFuncSetAttribute(matmul_bf16_tcgen05_kernel<BN, STAGES>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_set = true;
-  }
+  // per device (function attributes belong to the current context), cheap enough to repeat
+  B200K_CHECK_CUDA(cudaFuncSetAttribute(matmul_bf16_tcgen05_kernel<BN, STAGES>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
   matmul_bf16_tcgen05_kernel<BN, STAGES><<<grid, MM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p);
   count_launch();
