@@ -95,6 +95,25 @@ int b200k_matmul_bf16(const void* A, const void* B, void* C, int M, int N, int K
  */
 int b200k_attn_fwd_bf16(const void* q, const void* k, const void* v, void* o, float* lse2,
                         int Z, int H, int N_CTX, int D, int causal, float sm_scale, void* stream);
+/*
+ * The same attention forward for callers that cannot allocate device memory (no counterpart in the
+ * reference).  b200k_attn_fwd_bf16 makes its caller allocate the M buffer even when only O is wanted,
+ * and its first call on a device obtains the library's status word with cudaMalloc.  Hosts that run
+ * under an allocator they must not bypass, plugins that only ever see buffers handed to them, and warm
+ * serving loops that may not allocate can call this entry point instead: M and the status word live in
+ * a static device array inside the library (2 MiB + 256 B on every GPU that loads it, held until exit),
+ * and the call performs no cudaMalloc, cudaFree or other allocating call.  O is identical to
+ * b200k_attn_fwd_bf16's; M is not returned.
+ *   - Limit: Z*H*N_CTX <= 524288 query rows (the static array's capacity); larger problems are rejected
+ *     with B200K_ERR_INVALID_ARG.  Other argument rules are those of b200k_attn_fwd_bf16.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress) with that
+ *     device current; make that first call before any stream capture begins.
+ *   - All calls on one device share the array.  Each call zeroes the status block on `stream` before the
+ *     kernel; two calls whose kernels overlap on the GPU (different streams) race on it and on the row
+ *     statistics, so serialise calls per device.
+ */
+int b200k_attn_fwd_bf16_noalloc(const void* q, const void* k, const void* v, void* o,
+                                int Z, int H, int N_CTX, int D, int causal, float sm_scale, void* stream);
 /* 1 if b200k_attn_fwd_bf16 has a kernel for this (D, N_CTX), else 0. */
 int b200k_attn_supported(int D, int N_CTX);
 

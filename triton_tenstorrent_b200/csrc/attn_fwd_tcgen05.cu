@@ -22,6 +22,9 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "launch.h"
 #include "ptx.cuh"
 
@@ -501,3 +504,87 @@ int attn_fwd_bf16(const AttnArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace b200k
+
+// ---------------------------------------------------------------------------------------------
+// Attention forward for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------
+// b200k_attn_fwd_bf16 needs two pieces of device memory besides q, k, v and o: the row statistics
+// M (one fp32 per query row, which the caller must allocate even when it only wants O) and the
+// library's status word, which the first call on a device obtains with cudaMalloc.  Some callers can
+// do neither: code running under a memory pool that forbids raw CUDA allocations, a plugin that is
+// handed fixed buffers by its host application, or a serving loop that must not touch the allocator
+// once it is warm.  For them the same kernel is launched with both pieces placed in the static device
+// array below, which every GPU that loads this library holds from module load until exit.
+//
+// Layout: words [0, 64) status block (the kernel uses word 0), then one fp32 per query row.
+#define B200K_ATTN_NOALLOC_MAX_ROWS 524288  /* Z*H*N_CTX; 2 MiB of row statistics (+256 B) per GPU */
+static __device__ __align__(256) uint32_t g_attn_noalloc_scratch[64 + B200K_ATTN_NOALLOC_MAX_ROWS];
+
+namespace b200k {
+
+struct NoAllocDevice {
+  uint32_t* scratch;  // device address of g_attn_noalloc_scratch on that device
+  int sm_count;
+  int cc_major;
+};
+static NoAllocDevice g_noalloc_dev[64];
+static std::atomic<int> g_noalloc_ready[64];
+static std::mutex g_noalloc_mutex;
+
+// Per-device set-up (first call on a device, with that device current): the array's name is only a
+// host-side handle, so its device address is looked up once and cached.  Nothing is allocated.
+static const NoAllocDevice* noalloc_device() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error(B200K_ERR_NO_DEVICE, "attention (no-alloc): no usable current device (%s)", cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (g_noalloc_ready[dev].load(std::memory_order_acquire)) return &g_noalloc_dev[dev];
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ready[dev].load(std::memory_order_acquire)) return &g_noalloc_dev[dev];
+  NoAllocDevice d{};
+  void* ptr = nullptr;
+  e = cudaGetSymbolAddress(&ptr, g_attn_noalloc_scratch);
+  if (e != cudaSuccess || ptr == nullptr) {
+    set_error(B200K_ERR_CUDA, "attention (no-alloc): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  d.scratch = static_cast<uint32_t*>(ptr);
+  if ((e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+      (e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) {
+    set_error(B200K_ERR_CUDA, "attention (no-alloc): cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  g_noalloc_dev[dev] = d;
+  g_noalloc_ready[dev].store(1, std::memory_order_release);
+  return &g_noalloc_dev[dev];
+}
+
+}  // namespace b200k
+
+extern "C" int b200k_attn_fwd_bf16_noalloc(const void* q, const void* k, const void* v, void* o, int Z, int H, int N_CTX,
+                                           int D, int causal, float sm_scale, void* stream) {
+  using namespace b200k;
+  clear_error();
+  const int64_t rows = static_cast<int64_t>(Z) * H * N_CTX;
+  if (Z > 0 && H > 0 && N_CTX > 0 && rows > B200K_ATTN_NOALLOC_MAX_ROWS)
+    return set_error(B200K_ERR_INVALID_ARG,
+                     "attention (no-alloc): Z*H*N_CTX = %lld query rows exceed the %d rows the static scratch holds; "
+                     "split the batch or use b200k_attn_fwd_bf16 with a caller-provided M buffer",
+                     (long long)rows, B200K_ATTN_NOALLOC_MAX_ROWS);
+  // dummy non-null M so that the shared checks apply unchanged; replaced below
+  AttnArgs a{q, k, v, o, reinterpret_cast<float*>(uintptr_t(16)), Z, H, N_CTX, D, causal, sm_scale};
+  const int rc = attn_check_args(a);
+  if (rc != B200K_OK) return rc;
+  const NoAllocDevice* dev = noalloc_device();
+  if (dev == nullptr) return B200K_ERR_NO_DEVICE;
+  if (dev->cc_major != 10) return set_error(B200K_ERR_NO_DEVICE, "attention (no-alloc): needs an sm_100 device");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the status block must start at zero (the kernel records only the first failure); the row
+  // statistics are write-only and need no clearing
+  B200K_CHECK_CUDA(cudaMemsetAsync(dev->scratch, 0, 64 * sizeof(uint32_t), s));
+  a.lse2 = reinterpret_cast<float*>(dev->scratch + 64);
+  return attn_launch(a, s, dev->sm_count, dev->scratch);
+}
+
