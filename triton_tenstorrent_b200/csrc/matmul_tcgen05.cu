@@ -73,6 +73,102 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   return x;
 }
 
+// One 64-column chunk of a warp's 32 accumulator rows: fused bias / activation / downcast, swizzled
+// staging in shared memory, TMA store.  v0/v1 hold columns [0,32) and [32,64) of the chunk as fp32
+// bits; `row` is this thread's global row, `row0_warp` the warp's first row, `col0` the chunk's
+// first global column; `buf` toggles between the warp's two staging buffers.
+__device__ __forceinline__ void epilogue_chunk(const MatmulParams& p, const CUtensorMap* tmap_c,
+                                               const uint32_t (&v0)[32], const uint32_t (&v1)[32], int row,
+                                               int row0_warp, int col0, uint8_t* my_stage, int& buf, uint32_t lane) {
+    float f[64];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      f[j] = __uint_as_float(v0[j]);
+      f[32 + j] = __uint_as_float(v1[j]);
+    }
+    // ---- fused epilogue
+    if (p.bias_row != nullptr) {
+      if (col0 + 64 <= p.N) {
+        const float4* bp = reinterpret_cast<const float4*>(p.bias_row + col0);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float4 b = __ldg(bp + j);
+          f[4 * j + 0] += b.x;
+          f[4 * j + 1] += b.y;
+          f[4 * j + 2] += b.z;
+          f[4 * j + 3] += b.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (col0 + j < p.N) f[j] += __ldg(p.bias_row + col0 + j);
+      }
+    }
+    float bfull[64];
+    const bool has_full = (p.bias_full != nullptr);
+    if (has_full) {
+      const bool row_ok = row < p.M;
+      const uint16_t* brow = p.bias_full + static_cast<int64_t>(row_ok ? row : 0) * p.ldbias + col0;
+      if (row_ok && col0 + 64 <= p.N && (p.ldbias & 7) == 0 &&
+          (reinterpret_cast<uintptr_t>(p.bias_full) & 15u) == 0) {
+        const uint4* bp = reinterpret_cast<const uint4*>(brow);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 b = __ldg(bp + j);
+          bfull[8 * j + 0] = bf16_bits_to_f32(b.x & 0xFFFFu);
+          bfull[8 * j + 1] = bf16_bits_to_f32(b.x >> 16);
+          bfull[8 * j + 2] = bf16_bits_to_f32(b.y & 0xFFFFu);
+          bfull[8 * j + 3] = bf16_bits_to_f32(b.y >> 16);
+          bfull[8 * j + 4] = bf16_bits_to_f32(b.z & 0xFFFFu);
+          bfull[8 * j + 5] = bf16_bits_to_f32(b.z >> 16);
+          bfull[8 * j + 6] = bf16_bits_to_f32(b.w & 0xFFFFu);
+          bfull[8 * j + 7] = bf16_bits_to_f32(b.w >> 16);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          bfull[j] = (row_ok && col0 + j < p.N) ? bf16_bits_to_f32(__ldg(brow + j)) : 0.f;
+      }
+      if (!p.round_before_bias) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) f[j] += bfull[j];
+      }
+    }
+    if (p.act != B200K_ACT_NONE) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) f[j] = apply_act(f[j], p.act);
+    }
+    uint32_t packed[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+    if (has_full && p.round_before_bias) {
+      // 16-bit add after the downcast: bf16(float(bf16(acc)) + float(bias))
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float lo = bf16_bits_to_f32(packed[j] & 0xFFFFu) + bfull[2 * j];
+        const float hi = bf16_bits_to_f32(packed[j] >> 16) + bfull[2 * j + 1];
+        packed[j] = pack_bf16x2(lo, hi);
+      }
+    }
+    // ---- staging buffer `buf` must no longer be read by the TMA store issued two chunks ago
+    if (lane == 0) tma_store_wait_read<1>();
+    __syncwarp();
+    uint8_t* dst = my_stage + buf * MM_C_BUF_BYTES + lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+      *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = val;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (row0_warp < p.M && col0 < p.N)
+        tma_store_2d(tmap_c, my_stage + buf * MM_C_BUF_BYTES, col0, row0_warp);
+      tma_store_commit();
+    }
+    buf ^= 1;
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(MM_THREADS, 1)
 matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -209,94 +305,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
         }
-        const int col0 = n0 + c * 64;
-        float f[64];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          f[j] = __uint_as_float(v0[j]);
-          f[32 + j] = __uint_as_float(v1[j]);
-        }
-        // ---- fused epilogue
-        if (p.bias_row != nullptr) {
-          if (col0 + 64 <= p.N) {
-            const float4* bp = reinterpret_cast<const float4*>(p.bias_row + col0);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float4 b = __ldg(bp + j);
-              f[4 * j + 0] += b.x;
-              f[4 * j + 1] += b.y;
-              f[4 * j + 2] += b.z;
-              f[4 * j + 3] += b.w;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 64; ++j)
-              if (col0 + j < p.N) f[j] += __ldg(p.bias_row + col0 + j);
-          }
-        }
-        float bfull[64];
-        const bool has_full = (p.bias_full != nullptr);
-        if (has_full) {
-          const bool row_ok = row < p.M;
-          const uint16_t* brow = p.bias_full + static_cast<int64_t>(row_ok ? row : 0) * p.ldbias + col0;
-          if (row_ok && col0 + 64 <= p.N && (p.ldbias & 7) == 0 &&
-              (reinterpret_cast<uintptr_t>(p.bias_full) & 15u) == 0) {
-            const uint4* bp = reinterpret_cast<const uint4*>(brow);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const uint4 b = __ldg(bp + j);
-              bfull[8 * j + 0] = bf16_bits_to_f32(b.x & 0xFFFFu);
-              bfull[8 * j + 1] = bf16_bits_to_f32(b.x >> 16);
-              bfull[8 * j + 2] = bf16_bits_to_f32(b.y & 0xFFFFu);
-              bfull[8 * j + 3] = bf16_bits_to_f32(b.y >> 16);
-              bfull[8 * j + 4] = bf16_bits_to_f32(b.z & 0xFFFFu);
-              bfull[8 * j + 5] = bf16_bits_to_f32(b.z >> 16);
-              bfull[8 * j + 6] = bf16_bits_to_f32(b.w & 0xFFFFu);
-              bfull[8 * j + 7] = bf16_bits_to_f32(b.w >> 16);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 64; ++j)
-              bfull[j] = (row_ok && col0 + j < p.N) ? bf16_bits_to_f32(__ldg(brow + j)) : 0.f;
-          }
-          if (!p.round_before_bias) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) f[j] += bfull[j];
-          }
-        }
-        if (p.act != B200K_ACT_NONE) {
-#pragma unroll
-          for (int j = 0; j < 64; ++j) f[j] = apply_act(f[j], p.act);
-        }
-        uint32_t packed[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
-        if (has_full && p.round_before_bias) {
-          // 16-bit add after the downcast: bf16(float(bf16(acc)) + float(bias))
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float lo = bf16_bits_to_f32(packed[j] & 0xFFFFu) + bfull[2 * j];
-            const float hi = bf16_bits_to_f32(packed[j] >> 16) + bfull[2 * j + 1];
-            packed[j] = pack_bf16x2(lo, hi);
-          }
-        }
-        // ---- staging buffer `buf` must no longer be read by the TMA store issued two chunks ago
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
-        uint8_t* dst = my_stage + buf * MM_C_BUF_BYTES + lane * 128;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-          *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = val;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (m0 + q * 32 < p.M && col0 < p.N)
-            tma_store_2d(&tmap_c, my_stage + buf * MM_C_BUF_BYTES, col0, m0 + q * 32);
-          tma_store_commit();
-        }
-        buf ^= 1;
+        epilogue_chunk(p, &tmap_c, v0, v1, row, m0 + q * 32, n0 + c * 64, my_stage, buf, lane);
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
@@ -309,6 +318,201 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
   if (warp_idx == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// =============================================================================================
+// CTA-pair variant (cta_group::2): two CTAs of a cluster share one 256 x 256 output tile.
+// CTA r of the pair loads its own 128 rows of A and its own 128-column half of B (so each SM moves
+// 32 KB per K block instead of 48 KB), the pair leader issues one M = 256 MMA per K step that reads
+// both CTAs' shared memory, and each CTA's tensor memory receives its 128 rows x 256 columns of the
+// accumulator.  Loads of both CTAs are counted on the leader's "full" barrier; the leader's commits
+// release the ring slot in both CTAs and publish the accumulator to both epilogues.
+// =============================================================================================
+constexpr int MM2_BN = 256;                                  // tile columns (both CTAs)
+constexpr int MM2_B_STAGE_BYTES = 2 * MM_B_BOX_BYTES;        // this CTA's 64 x 128 half of B: 16 KB
+constexpr int MM2_STAGE_BYTES = MM_A_STAGE_BYTES + MM2_B_STAGE_BYTES;  // 32 KB per CTA per K block
+
+template <int STAGES>
+struct Matmul2Smem {
+  static constexpr int A_OFF = 0;
+  static constexpr int B_OFF = STAGES * MM_A_STAGE_BYTES;
+  static constexpr int C_OFF = B_OFF + STAGES * MM2_B_STAGE_BYTES;
+  static constexpr int BAR_OFF = C_OFF + MM_C_STAGING_BYTES;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int TOTAL = BAR_OFF + BAR_BYTES + 1024;
+};
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MM_THREADS, 1)
+matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                const __grid_constant__ CUtensorMap tmap_c, const MatmulParams p) {
+  using L = Matmul2Smem<STAGES>;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t IDESC = umma_idesc_bf16_f32(256, MM2_BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem + L::A_OFF;
+  uint8_t* smem_b = smem + L::B_OFF;
+  uint8_t* smem_c = smem + L::C_OFF;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);   // used in the leader only
+  uint64_t* empty_bar = full_bar + STAGES;                               // one set per CTA
+  uint64_t* tmem_full_bar = empty_bar + STAGES;                          // one set per CTA
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;                          // used in the leader only
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  uint32_t* abort_smem = tmem_ptr_smem + 1;
+
+  const int warp_idx = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  const uint32_t rank = cluster_ctarank();      // 0 = pair leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  WaitCtx ctx{abort_smem, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);       // the leader's producer arrives once (with the byte count of both CTAs)
+      mbar_init(&empty_bar[s], 1);      // one commit from the leader's MMA thread
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);                   // one commit from the leader's MMA thread
+      mbar_init(&tmem_empty_bar[a], 2 * MM_EPI_WARPS);   // epilogue warps of both CTAs
+    }
+    *abort_smem = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_c);
+  }
+  if (warp_idx == 1) {
+    tmem_alloc_2cta(tmem_ptr_smem, TMEM_COLS);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  __syncthreads();
+  // both CTAs' barriers must exist before either CTA signals the other
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp_idx == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+      int pid_m, pid_n;
+      tile_coords(p, tile, pid_m, pid_n);
+      const int m0 = pid_m * 256 + static_cast<int>(rank) * MM_BM;
+      const int n0 = pid_n * MM2_BN + static_cast<int>(rank) * 128;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = mbar_wait(&empty_bar[stage], phase ^ 1u, ctx, 41);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t leader_full = mapa_shared(smem_u32(&full_bar[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * MM2_STAGE_BYTES);
+          tma_load_2d_2cta(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, leader_full, kb * MM_BK, m0);
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            tma_load_2d_2cta(smem_b + stage * MM2_B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, leader_full,
+                             n0 + i * 64, kb * MM_BK);
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp_idx == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader only)
+    if (rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, ctx, 42);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * MM2_BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, ctx, 43);
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_addr = smem_u32(smem_a + stage * MM_A_STAGE_BYTES);
+            const uint32_t b_addr = smem_u32(smem_b + stage * MM2_B_STAGE_BYTES);
+#pragma unroll
+            for (int k = 0; k < MM_BK / MM_UMMA_K; ++k) {
+              const uint64_t a_desc = umma_smem_desc_sw128(a_addr + k * (MM_UMMA_K * 2), 16, 1024);
+              const uint64_t b_desc = umma_smem_desc_sw128(b_addr + k * (MM_UMMA_K * 128), MM_B_BOX_BYTES, 1024);
+              umma_ss_2cta(d_tmem, a_desc, b_desc, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            // release this ring slot in both CTAs once the MMAs above have read it
+            const uint32_t e = smem_u32(&empty_bar[stage]);
+            umma_commit_2cta(mapa_shared(e, 0));
+            umma_commit_2cta(mapa_shared(e, 1));
+            if (kb == p.num_kb - 1) {  // accumulator complete: wake both epilogues
+              const uint32_t f = smem_u32(&tmem_full_bar[acc]);
+              umma_commit_2cta(mapa_shared(f, 0));
+              umma_commit_2cta(mapa_shared(f, 1));
+            }
+          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5, both CTAs)
+    const int q = warp_idx & 3;
+    const int ew = warp_idx - 2;
+    uint8_t* my_stage = smem_c + ew * 2 * MM_C_BUF_BYTES;
+    int it = 0;
+    int buf = 0;
+    bool ok = true;
+    for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++it) {
+      int pid_m, pid_n;
+      tile_coords(p, tile, pid_m, pid_n);
+      const int m0 = pid_m * 256 + static_cast<int>(rank) * MM_BM;
+      const int n0 = pid_n * MM2_BN;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(&tmem_full_bar[acc], acc_phase, ctx, 44);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + static_cast<int>(lane);
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MM2_BN;
+#pragma unroll 1
+      for (int c = 0; c < MM2_BN / 64; ++c) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_x32(t_row + c * 64, v0);
+        tmem_ld_x32(t_row + c * 64 + 32, v1);
+        tmem_wait_ld();
+        if (c == MM2_BN / 64 - 1) {
+          // this warp's part of the accumulator has left tensor memory: tell the leader's MMA thread
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));
+        }
+        epilogue_chunk(p, &tmap_c, v0, v1, row, m0 + q * 32, n0 + c * 64, my_stage, buf, lane);
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  // Neither CTA may exit (or free tensor memory) while its partner can still signal its barriers.
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp_idx == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
   }
 }
 
@@ -329,7 +533,7 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.num_pid_m = (a.M + MM_BM - 1) / MM_BM;
   p.num_pid_n = (a.N + BN - 1) / BN;
-  p.group_m = 8;
+  p.group_m = 16;  // 16 tile rows of 128 = 2048 rows of A (33.5 MB at K = 8192) stay hot in L2
   if (const char* g = getenv("B200K_MATMUL_GROUP_M")) { int v = atoi(g); if (v > 0) p.group_m = v; }
   p.num_tiles = p.num_pid_m * p.num_pid_n;
   p.num_kb = (a.K + MM_BK - 1) / MM_BK;
@@ -357,6 +561,42 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   return B200K_OK;
 }
 
+template <int STAGES>
+static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_t stream, uint32_t* status) {
+  using L = Matmul2Smem<STAGES>;
+  static_assert(L::TOTAL <= 232448, "shared memory budget exceeded");
+  CUtensorMap ta, tb, tc;
+  int rc;
+  if ((rc = make_tmap_bf16_2d(&ta, a.A, a.K, a.M, a.lda, 64, MM_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tb, a.B, a.N, a.K, a.ldb, 64, MM_BK)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tc, a.C, a.N, a.M, a.ldc, 64, 32)) != 0) return rc;
+
+  MatmulParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.num_pid_m = (a.M + 255) / 256;
+  p.num_pid_n = (a.N + MM2_BN - 1) / MM2_BN;
+  p.group_m = 8;  // 8 tile rows of 256 = 2048 rows of A stay hot in L2 while the tile columns stream
+  if (const char* g = getenv("B200K_MATMUL_GROUP_M")) { int v = atoi(g); if (v > 0) p.group_m = v; }
+  p.num_tiles = p.num_pid_m * p.num_pid_n;
+  p.num_kb = (a.K + MM_BK - 1) / MM_BK;
+  p.bias_row = (a.bias_kind == B200K_BIAS_ROW_F32) ? static_cast<const float*>(a.bias) : nullptr;
+  p.bias_full = (a.bias_kind == B200K_BIAS_FULL_BF16) ? static_cast<const uint16_t*>(a.bias) : nullptr;
+  p.ldbias = a.ldbias;
+  p.act = a.act;
+  p.round_before_bias = a.round_before_bias;
+  p.b_lbo = p.b_sbo = p.b_kstep = 0;  // fixed in the kernel
+  p.status = status;
+
+  B200K_CHECK_CUDA(cudaFuncSetAttribute(matmul_bf16_tcgen05_2cta_kernel<STAGES>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+  const int max_pairs = dev->sm_count / 2;
+  const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  matmul_bf16_tcgen05_2cta_kernel<STAGES><<<2 * pairs, MM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p);
+  count_launch();
+  B200K_CHECK_LAUNCH("matmul_bf16_tcgen05_2cta_kernel");
+  return B200K_OK;
+}
+
 int matmul_bf16(const MatmulArgs& a, cudaStream_t stream, uint32_t* status_override) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) return set_error(B200K_ERR_INVALID_ARG, "matmul: M, N, K must be positive (got %d, %d, %d)", a.M, a.N, a.K);
   if (a.A == nullptr || a.B == nullptr || a.C == nullptr) return set_error(B200K_ERR_INVALID_ARG, "matmul: null operand pointer");
@@ -381,6 +621,11 @@ int matmul_bf16(const MatmulArgs& a, cudaStream_t stream, uint32_t* status_overr
   const int64_t tiles256 = static_cast<int64_t>((a.M + MM_BM - 1) / MM_BM) * ((a.N + 255) / 256);
   bool narrow = (a.N <= 128) || (tiles256 < dev->sm_count);
   if (const char* f = getenv("B200K_MATMUL_BN")) { int v = atoi(f); if (v == 128) narrow = true; if (v == 256) narrow = false; }
+  // CTA pairs on 256 x 256 tiles when there are enough of them to occupy every pair of SMs.
+  const int64_t tiles2 = static_cast<int64_t>((a.M + 255) / 256) * ((a.N + 255) / 256);
+  bool pair = tiles2 >= dev->sm_count / 2;
+  if (const char* f = getenv("B200K_MATMUL_2CTA")) pair = atoi(f) != 0;
+  if (pair) return launch_matmul_2cta<6>(a, dev, stream, status);
   if (narrow) return launch_matmul<128, 6>(a, dev, stream, status);
   return launch_matmul<256, 4>(a, dev, stream, status);
 }
