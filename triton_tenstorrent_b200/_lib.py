@@ -5,10 +5,12 @@ There is no fallback: if the library is missing or a call fails, an exception is
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, Union, c_char, c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libb200kernels.so"
+# B200K_LIBRARY selects another build of the same library (e.g. one compiled with debug defines).
+LIB_PATH = Path(os.environ.get("B200K_LIBRARY") or Path(__file__).resolve().parent / "libb200kernels.so")
 
 OK = 0
 ERR_INVALID_ARG = -1

@@ -7,6 +7,7 @@
 //   warps 0-3   softmax group of Q tile 0     warps 4-7   softmax group of Q tile 1
 //   warp 8      TMA producer (Q tiles, K/V ring of 32 KB slots in the order K0 V0 K1 V1 ...)
 //   warp 9      tensor-memory owner and tcgen05.mma issuer
+//   warps 10-11 idle (they complete the third warpgroup so that it can release registers)
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  S = Q K^T is produced
 // by an SS MMA; each softmax thread owns one row (tcgen05.ld 32x32b), so row max / row sum need no
 // cross-thread exchange; P is rounded to bf16 (the reference's p.to(dtype), :81) and written back
@@ -33,7 +34,7 @@ namespace b200k {
 constexpr int AT_BM = 128;            // rows per Q tile
 constexpr int AT_BN = 128;            // keys per K/V block
 constexpr int AT_D = 128;             // head dimension
-constexpr int AT_THREADS = 320;
+constexpr int AT_THREADS = 384;         // three warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
 constexpr int AT_TILE_BYTES = AT_BM * AT_D * 2;  // 32 KB: two 16 KB boxes of 64 columns
 constexpr int AT_BOX_BYTES = 16384;
 constexpr int AT_NSLOT = 5;           // K/V ring slots
@@ -81,6 +82,14 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+// 12 warps start with 168 registers each (16384 per scheduler partition / 96 threads).  The third
+// warpgroup then returns registers to the CTA's pool and the softmax warpgroups take them
+// (setmaxnreg), so that a softmax thread can hold a whole row of scores plus the packed P values
+// without spilling.  Only what the CTA was given at launch can be redistributed:
+// 2 x (216 - 168) = 168 - 72 per thread triple.
+constexpr int AT_REGS_SOFTMAX = 216;
+constexpr int AT_REGS_OTHER = 72;
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -135,7 +144,10 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  if (warp_idx == 8) {
+  // Each role's code is dominated by its warpgroup's setmaxnreg so that the compiler knows its budget.
+  if (warp_idx >= 8) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(AT_REGS_OTHER));  // all four warps, one instruction
+   if (warp_idx == 8) {
     // ------------------------------------------------------------------ TMA producer
     int slot = 0;
     uint32_t slot_phase = 0;
@@ -175,7 +187,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
       }
     }
-  } else if (warp_idx == 9) {
+   } else if (warp_idx == 9) {
     // ------------------------------------------------------------------ MMA issuer
     int slot = 0;                 // next ring slot to consume (K0 V0 K1 V1 ...)
     uint32_t slot_phase = 0;
@@ -276,8 +288,10 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         }
       }
     }
+   }  // warps 10 and 11 have no role
   } else {
     // ------------------------------------------------------------------ softmax groups (warps 0..7)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(AT_REGS_SOFTMAX));
     const int t = warp_idx >> 2;        // Q tile of this group
     const int q = warp_idx & 3;         // TMEM lane quarter
     const int r = q * 32 + static_cast<int>(lane);  // row within the tile
@@ -319,11 +333,11 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
-          mx1 = fmaxf(mx1, __uint_as_float(s1[c]));
-          mx2 = fmaxf(mx2, __uint_as_float(s2[c]));
-          mx3 = fmaxf(mx3, __uint_as_float(s3[c]));
+        for (int c = 0; c < 32; c += 2) {  // 3-input max: two new scores per instruction
+          mx0 = fmax3(mx0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+          mx2 = fmax3(mx2, __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
+          mx3 = fmax3(mx3, __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const float m_new = fmaxf(m_used, mx * scale);
@@ -345,17 +359,21 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
             }
           }
         }
-        const float neg_m = -m_used;
-        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        // p = exp2(s * scale - m): the multiply-subtract and the row sum run two lanes per instruction
+        // (fma.rn.f32x2 / add.rn.f32x2); each lane rounds exactly like the scalar fma / add.
+        const uint64_t scale2 = pack_f32x2(scale, scale);
+        const uint64_t negm2 = pack_f32x2(-m_used, -m_used);
+        uint64_t sum_a = 0, sum_b = 0;  // bit pattern of (0.f, 0.f)
         {
           uint32_t pk[32];
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
-            const float a0 = ex2_approx(fmaf(__uint_as_float(s0[2 * c]), scale, neg_m));
-            const float a1 = ex2_approx(fmaf(__uint_as_float(s0[2 * c + 1]), scale, neg_m));
-            const float b0 = ex2_approx(fmaf(__uint_as_float(s1[2 * c]), scale, neg_m));
-            const float b1 = ex2_approx(fmaf(__uint_as_float(s1[2 * c + 1]), scale, neg_m));
-            sum0 += a0; sum1 += a1; sum2 += b0; sum3 += b1;
+            float a0, a1, b0, b1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1])), scale2, negm2), a0, a1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s1[2 * c]), __uint_as_float(s1[2 * c + 1])), scale2, negm2), b0, b1);
+            a0 = ex2_approx(a0); a1 = ex2_approx(a1); b0 = ex2_approx(b0); b1 = ex2_approx(b1);
+            sum_a = add_f32x2(sum_a, pack_f32x2(a0, a1));
+            sum_b = add_f32x2(sum_b, pack_f32x2(b0, b1));
             pk[c] = pack_bf16x2(a0, a1);
             pk[16 + c] = pack_bf16x2(b0, b1);
           }
@@ -365,17 +383,23 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           uint32_t pk[32];
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
-            const float a0 = ex2_approx(fmaf(__uint_as_float(s2[2 * c]), scale, neg_m));
-            const float a1 = ex2_approx(fmaf(__uint_as_float(s2[2 * c + 1]), scale, neg_m));
-            const float b0 = ex2_approx(fmaf(__uint_as_float(s3[2 * c]), scale, neg_m));
-            const float b1 = ex2_approx(fmaf(__uint_as_float(s3[2 * c + 1]), scale, neg_m));
-            sum0 += a0; sum1 += a1; sum2 += b0; sum3 += b1;
+            float a0, a1, b0, b1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s2[2 * c]), __uint_as_float(s2[2 * c + 1])), scale2, negm2), a0, a1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s3[2 * c]), __uint_as_float(s3[2 * c + 1])), scale2, negm2), b0, b1);
+            a0 = ex2_approx(a0); a1 = ex2_approx(a1); b0 = ex2_approx(b0); b1 = ex2_approx(b1);
+            sum_a = add_f32x2(sum_a, pack_f32x2(a0, a1));
+            sum_b = add_f32x2(sum_b, pack_f32x2(b0, b1));
             pk[c] = pack_bf16x2(a0, a1);
             pk[16 + c] = pack_bf16x2(b0, b1);
           }
           tmem_st_x32(t_s + 32, pk);
         }
-        l += (sum0 + sum1) + (sum2 + sum3);
+        {
+          float sa0, sa1, sb0, sb1;
+          unpack_f32x2(sum_a, sa0, sa1);
+          unpack_f32x2(sum_b, sb0, sb1);
+          l += (sa0 + sa1) + (sb0 + sb1);
+        }
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
