@@ -37,9 +37,9 @@ M = N = K = 8192
 FLOP_PER_STEP = 2.0 * M * N * K
 METRIC = "bf16 matmul TFLOP/s (persistent tensor-descriptor matmul, M=N=K=8192 per GPU)"
 
-# DRAM traffic of one 8192^3 launch of matmul_bf16_tcgen05_kernel<256,4> from an ncu capture
-# (dram__bytes_read.sum 1.406 GB + dram__bytes_write.sum 127.4 MB; profiles/matmul_bf16_tcgen05_8192.md).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1_533_478_000
+# DRAM traffic of one 8192^3 launch of the headline kernel from an ncu capture
+# (dram__bytes_read.sum 1.104 GB + dram__bytes_write.sum 127.4 MB; profiles/matmul_bf16_tcgen05_2cta_8192.md).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1_231_452_000
 
 
 def measured_peaks():
@@ -111,6 +111,7 @@ def cpu_reference_rate(rows: int, repeat: int = 1):
     all host threads.  Returns (TFLOP/s, seconds, threads)."""
     import golden_inputs as gi
     from oracle import cpu_oracle as oracle
+    oracle.use_all_cores()
     a, b = gi.matmul_inputs(rows, N, K, seed=0)
     best = float("inf")
     for _ in range(repeat):
@@ -128,7 +129,7 @@ def run_reference(args, rank, world):
         return
     import golden_inputs as gi
     from oracle import cpu_oracle as oracle
-    threads = oracle.max_threads()
+    threads = oracle.use_all_cores()
     # calibrate on 8 rows, then size a step so that warmup + steps stay near two minutes in total
     rate, secs, _ = cpu_reference_rate(8)
     rows_per_sec = 8 / secs
@@ -259,7 +260,7 @@ def main():
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"{'sustained' if sustained else 'burst'} cuBLAS bf16, {peaks['source']}",
                 "frac_of_burst": achieved / peaks["bf16_tflops"], "frac_of_nominal_2250": achieved / 2250.0,
-                "kernel": "matmul_bf16_tcgen05_kernel<256,4>", "kernel_ms": kernel_ms}
+                "kernel": "matmul_bf16_tcgen05_2cta_kernel<6>", "kernel_ms": kernel_ms}
 
     # ---- end to end through the public wrapper with pinned host buffers
     a_pin, b_pin = a_host.pin_memory(), b_host.pin_memory()

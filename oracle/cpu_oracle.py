@@ -42,6 +42,8 @@ def load() -> ctypes.CDLL:
         build()
     lib = ctypes.CDLL(str(path))
     lib.oracle_max_threads.restype = c_int
+    lib.oracle_set_threads.argtypes = [c_int]
+    lib.oracle_set_threads.restype = None
     lib.oracle_block_range.argtypes = [c_int64, c_int, c_int, POINTER(c_int64), POINTER(c_int64)]
     lib.oracle_add_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int]
     lib.oracle_sin_f32.argtypes = [c_void_p, c_void_p, c_int64, c_int, c_int]
@@ -61,6 +63,13 @@ def load() -> ctypes.CDLL:
 
 def max_threads() -> int:
     return load().oracle_max_threads()
+
+
+def use_all_cores() -> int:
+    """Lets OpenMP use every host core even if OMP_NUM_THREADS says otherwise; returns the thread count."""
+    import os
+    load().oracle_set_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+    return max_threads()
 
 
 def _cpu(t: torch.Tensor, dtype=None) -> torch.Tensor:

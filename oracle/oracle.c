@@ -64,6 +64,15 @@ void oracle_block_range(int64_t num_blocks, int workers, int w, int64_t* start, 
   *end = s + base + (w < rem ? 1 : 0);
 }
 
+/* Overrides OMP_NUM_THREADS (launchers such as torchrun set it to 1 for every rank). */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

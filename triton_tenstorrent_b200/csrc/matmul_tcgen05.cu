@@ -42,6 +42,7 @@ struct MatmulParams {
   int act;
   int round_before_bias;
   uint32_t b_lbo, b_sbo, b_kstep;  // MN-major B descriptor strides (bytes)
+  int l2_hint;                     // CTA-pair kernel: 0 = no hints, 1 = A evict_last / B evict_first, 2 = A evict_last only
   uint32_t* status;
 };
 
@@ -402,6 +403,9 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    // The A row panel of a tile group is re-read by every tile column of the sweep; B tiles stream.
+    const uint64_t pol_a = p.l2_hint ? l2_policy_evict_last() : l2_policy_evict_normal();
+    const uint64_t pol_b = p.l2_hint == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
     for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
       int pid_m, pid_n;
       tile_coords(p, tile, pid_m, pid_n);
@@ -413,11 +417,11 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
         if (lane == 0) {
           const uint32_t leader_full = mapa_shared(smem_u32(&full_bar[stage]), 0);
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * MM2_STAGE_BYTES);
-          tma_load_2d_2cta(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, leader_full, kb * MM_BK, m0);
+          tma_load_2d_2cta_hint(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, leader_full, kb * MM_BK, m0, pol_a);
 #pragma unroll
           for (int i = 0; i < 2; ++i)
-            tma_load_2d_2cta(smem_b + stage * MM2_B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, leader_full,
-                             n0 + i * 64, kb * MM_BK);
+            tma_load_2d_2cta_hint(smem_b + stage * MM2_B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, leader_full,
+                                  n0 + i * 64, kb * MM_BK, pol_b);
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -549,6 +553,7 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
     unsigned l = 0, sb = 0, ks = 0;
     if (sscanf(dbg, "%u,%u,%u", &l, &sb, &ks) == 3) { p.b_lbo = l; p.b_sbo = sb; p.b_kstep = ks; }
   }
+  p.l2_hint = 0;
   p.status = status;
 
   // per device (function attributes belong to the current context), cheap enough to repeat
@@ -585,6 +590,8 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   p.act = a.act;
   p.round_before_bias = a.round_before_bias;
   p.b_lbo = p.b_sbo = p.b_kstep = 0;  // fixed in the kernel
+  p.l2_hint = 0;
+  if (const char* h = getenv("B200K_MATMUL_L2_HINT")) p.l2_hint = atoi(h);
   p.status = status;
 
   B200K_CHECK_CUDA(cudaFuncSetAttribute(matmul_bf16_tcgen05_2cta_kernel<STAGES>,
