@@ -142,6 +142,21 @@ def test_matmul_oracle_shapes_and_tails(shape):
     assert oracle.pcc(got.float(), ref.float()) > 0.97
 
 
+@pytest.mark.parametrize("shape", [(2200, 2312, 520), (2304, 2304, 64), (4096, 1288, 1000)])
+def test_matmul_cta_pair_kernel_tails(shape):
+    # enough 256 x 256 tiles for the CTA-pair kernel, with M, N and K tails (second CTA of a pair partly or
+    # wholly outside M; last tile column partly outside N; K not a multiple of 64)
+    M, N, K = shape
+    a, b, bias_full = gi.fused_inputs(M, N, K, seed=14)
+    c = torch.full((M, N), 7.5, dtype=torch.bfloat16, device="cuda")
+    got = ops._matmul_call(a.cuda(), b.cuda(), c=c).cpu()
+    ref = oracle.golden_matmul(a, b)
+    assert not torch.any(got == 7.5), "an element of C was left unwritten"
+    assert oracle.rel_frobenius(got.float(), ref.float()) <= MATMUL_REL_FRO
+    got = ops.matmul_tma_fused(a.cuda(), b.cuda(), bias_full.cuda()).cpu()
+    assert oracle.rel_frobenius(got.float(), oracle.golden_matmul(a, b, bias=bias_full, mode=2).float()) <= MATMUL_REL_FRO
+
+
 def test_matmul_strided_operands_and_canaries():
     M, N, K = 300, 200, 264
     a, b = gi.matmul_inputs(M, N, K, seed=4)

@@ -590,7 +590,7 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   p.act = a.act;
   p.round_before_bias = a.round_before_bias;
   p.b_lbo = p.b_sbo = p.b_kstep = 0;  // fixed in the kernel
-  p.l2_hint = 0;
+  p.l2_hint = 2;  // keep the group's A row panel in L2 (measured +2 % at 8192^3 over no hint; B evict_first loses)
   if (const char* h = getenv("B200K_MATMUL_L2_HINT")) p.l2_hint = atoi(h);
   p.status = status;
 
