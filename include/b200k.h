@@ -86,6 +86,18 @@ int b200k_matmul_bf16(const void* A, const void* B, void* C, int M, int N, int K
                       int act, int round_before_bias, void* stream);
 
 /*
+ * The same contraction and epilogues with fp16 operands (A, B, C and a full [M,N] bias in fp16; fp32
+ * accumulate, one round-to-nearest-even to fp16).  The reference's matmul_kernel_fused hard-codes fp16
+ * (python/tutorials/09-matmul-fused.py:115) and its pointer-based matmul_kernel stores fp16
+ * (examples/matmul/03-matrix-multiplication.py:374,410); its fp16 tensor-descriptor twin is
+ * examples/matmul_tensor_descriptor/09-persistent-matmul.py:107-145.
+ */
+int b200k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K,
+                     int64_t lda, int64_t ldb, int64_t ldc,
+                     const void* bias, int bias_kind, int64_t ldbias,
+                     int act, int round_before_bias, void* stream);
+
+/*
  * O = softmax(Q K^T * sm_scale [+ causal mask]) V per (batch, head); q,k,v,o bf16 contiguous
  * [Z,H,N_CTX,D]; lse2[Z,H,N_CTX] fp32 receives m_i + log2(l_i) (base-2 log-sum-exp of the
  * scaled scores), exactly the `M` tensor of the reference.  D must be 128 (64 also accepted if
@@ -122,7 +134,9 @@ int b200k_attn_supported(int D, int N_CTX);
  * (backend/driver.py:98-170 TTLauncher.__call__: constexprs dropped, tensors as pointers,
  * TensorDescriptor flattened to base, shape.., strides.., padding flag, shape.., strides..).
  * kernel_name is one of: "add_kernel", "sin_kernel", "mul_add_kernel", "matmul_kernel_tma",
- * "matmul_kernel_fused", "_attn_fwd".  The grid is validated against the problem size
+ * "matmul_kernel_fused", "_attn_fwd", optionally followed by ":KEY=VALUE,..." with the constexpr values
+ * the reference bakes into the compiled kernel (BLOCK_SIZE, BLOCK_SIZE_M/N, STAGE, and F16=1 for the
+ * matmul kernels when the descriptors point at fp16 data).  The grid is validated against the problem size
  * implied by the arguments; it does not change the result.
  */
 typedef enum b200k_arg_kind { B200K_ARG_PTR = 0, B200K_ARG_I32 = 1, B200K_ARG_I64 = 2, B200K_ARG_F32 = 3 } b200k_arg_kind;

@@ -227,6 +227,47 @@ def test_matmul_fused_workload_shape_sample():
     assert oracle.rel_frobenius(got[rows.cuda()].cpu().float(), ref.float()) <= MATMUL_REL_FRO
 
 
+# fp16: the reference's fused kernel and its pointer-based example compute in fp16
+@pytest.mark.parametrize("shape", gi.FUSED_SHAPES)
+def test_matmul_fused_fp16_golden(golden_dir, shape):
+    # golden vectors made by running the reference's matmul_kernel_fused (python/tutorials/09-matmul-fused.py:105-148)
+    M, N, K = shape
+    g = np.load(golden_dir / "matmul_fused.npz")
+    a, b, bias = gi.fused_inputs(M, N, K, dtype=torch.float16)
+    golden = torch.from_numpy(g[f"c_{M}x{N}x{K}"])
+    got = ops.matmul_tma_fused(a.cuda(), b.cuda(), bias.cuda(), True).cpu()       # add after the downcast, like the kernel
+    assert got.dtype == torch.float16
+    assert oracle.rel_frobenius(got.float(), golden.float()) <= MATMUL_REL_FRO
+    diff = (got.float() - golden.float()).abs()
+    assert float(diff.max()) <= float(golden.float().abs().max()) * 2 ** -10       # one fp16 ulp of the largest value
+    assert float((diff > 0).float().mean()) < 5e-3
+    # the same through the kernel[grid] surface with descriptors over fp16 tensors
+    ad, bd, biasd = a.cuda(), b.cuda(), bias.cuda()
+    c = torch.full((M, N), 7.5, device="cuda", dtype=torch.float16)
+    descs = [TensorDescriptor.from_tensor(t, [32, 32]) for t in (ad, bd, c, biasd)]
+    mgrid = lambda META: (-(-M // META["BLOCK_SIZE_M"]) * -(-N // META["BLOCK_SIZE_N"]),)
+    kernels.matmul_kernel_fused[mgrid](*descs, M, N, K, FP8_OUTPUT=False, WARP_SPECIALIZE=True)
+    assert torch.equal(c.cpu().view(torch.int16), got.view(torch.int16))
+
+
+def test_matmul_fp16_example_shapes_and_activation():
+    # the reference's unit test of matmul(a, b): 32x64 . 64x32 fp16, atol 1e-2
+    # (examples/matmul/03-matrix-multiplication.py:431-438), plus larger shapes and leaky_relu
+    torch.manual_seed(0)
+    a = torch.rand((32, 64), dtype=torch.float16) - 0.5
+    b = torch.rand((64, 32), dtype=torch.float16) - 0.5
+    got = ops.matmul(a.cuda(), b.cuda()).cpu()
+    assert got.dtype == torch.float16
+    assert torch.allclose(got.float(), oracle.golden_matmul(a, b).float(), atol=1e-2, rtol=0)
+    for (M, N, K) in ((512, 384, 640), (2304, 2304, 136)):
+        a, b = gi.matmul_inputs(M, N, K, seed=15, dtype=torch.float16)
+        for act in ("", "leaky_relu"):
+            got = ops.matmul(a.cuda(), b.cuda(), activation=act).cpu()
+            ref = oracle.golden_matmul(a, b, mode=0, activation=act)
+            assert oracle.rel_frobenius(got.float(), ref.float()) <= MATMUL_REL_FRO
+            assert float((got.view(torch.int16) != ref.view(torch.int16)).float().mean()) < 1e-2
+
+
 def test_matmul_rejects_bad_arguments():
     a = torch.zeros(64, 36, dtype=torch.bfloat16, device="cuda")      # 72-byte rows
     b = torch.zeros(36, 64, dtype=torch.bfloat16, device="cuda")

@@ -266,6 +266,7 @@ static int generic_launch(const char* kernel_name, int gx, int gy, int gz, cudaS
       ma.bias = bias.base; ma.bias_kind = B200K_BIAS_FULL_BF16; ma.ldbias = bias.strides[0];
       ma.round_before_bias = 1;  // the Triton kernel adds the bias after the downcast
     }
+    ma.dtype = spec_value(spec, "F16", 0) ? 1 : 0;  // descriptors do not carry the element type
     return matmul_bf16(ma, stream, nullptr);
   }
   if (name == "_attn_fwd") {
@@ -333,7 +334,14 @@ int b200k_mul_add_f32(const float* x, const float* y, const float* z, float* out
 int b200k_matmul_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                       const void* bias, int bias_kind, int64_t ldbias, int act, int round_before_bias, void* stream) {
   clear_error();
-  MatmulArgs a{A, B, C, M, N, K, lda, ldb, ldc, bias, bias_kind, ldbias, act, round_before_bias};
+  MatmulArgs a{A, B, C, M, N, K, lda, ldb, ldc, bias, bias_kind, ldbias, act, round_before_bias, 0};
+  return matmul_bf16(a, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int b200k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                     const void* bias, int bias_kind, int64_t ldbias, int act, int round_before_bias, void* stream) {
+  clear_error();
+  MatmulArgs a{A, B, C, M, N, K, lda, ldb, ldc, bias, bias_kind, ldbias, act, round_before_bias, 1};
   return matmul_bf16(a, static_cast<cudaStream_t>(stream), nullptr);
 }
 

@@ -59,6 +59,7 @@ struct MatmulArgs {
   int64_t ldbias;
   int act;
   int round_before_bias;
+  int dtype;  // 0 = bf16, 1 = fp16 (A, B, C and a full [M,N] bias)
 };
 // status_override: device word the kernel reports bounded-wait failures to (nullptr = the
 // per-device word from current_device_info()).

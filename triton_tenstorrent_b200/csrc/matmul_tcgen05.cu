@@ -42,6 +42,8 @@ struct MatmulParams {
   int act;
   int round_before_bias;
   uint32_t b_lbo, b_sbo, b_kstep;  // MN-major B descriptor strides (bytes)
+  int f16;                         // operands, bias[M,N] and C are fp16 instead of bf16
+  uint32_t idesc;                  // UMMA instruction descriptor (tile shape, operand formats and majors)
   int l2_hint;                     // CTA-pair kernel: 0 = no hints, 1 = A evict_last / B evict_first, 2 = A evict_last only
   uint32_t* status;
 };
@@ -66,6 +68,14 @@ __device__ __forceinline__ void tile_coords(const MatmulParams& p, int tile, int
   const int in_group = tile - group_id * num_pid_in_group;
   pid_m = first_pid_m + (in_group % group_size_m);
   pid_n = in_group / group_size_m;
+}
+
+// 16-bit element <-> fp32 in the operand type of the launch (bf16 or fp16; warp-uniform flag)
+__device__ __forceinline__ float h16_to_f32(uint32_t bits16, int f16) {
+  return f16 ? f16_bits_to_f32(bits16) : bf16_bits_to_f32(bits16);
+}
+__device__ __forceinline__ uint32_t pack_h16x2(float lo, float hi, int f16) {
+  return f16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
 }
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -116,19 +126,19 @@ __device__ __forceinline__ void epilogue_chunk(const MatmulParams& p, const CUte
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const uint4 b = __ldg(bp + j);
-          bfull[8 * j + 0] = bf16_bits_to_f32(b.x & 0xFFFFu);
-          bfull[8 * j + 1] = bf16_bits_to_f32(b.x >> 16);
-          bfull[8 * j + 2] = bf16_bits_to_f32(b.y & 0xFFFFu);
-          bfull[8 * j + 3] = bf16_bits_to_f32(b.y >> 16);
-          bfull[8 * j + 4] = bf16_bits_to_f32(b.z & 0xFFFFu);
-          bfull[8 * j + 5] = bf16_bits_to_f32(b.z >> 16);
-          bfull[8 * j + 6] = bf16_bits_to_f32(b.w & 0xFFFFu);
-          bfull[8 * j + 7] = bf16_bits_to_f32(b.w >> 16);
+          bfull[8 * j + 0] = h16_to_f32(b.x & 0xFFFFu, p.f16);
+          bfull[8 * j + 1] = h16_to_f32(b.x >> 16, p.f16);
+          bfull[8 * j + 2] = h16_to_f32(b.y & 0xFFFFu, p.f16);
+          bfull[8 * j + 3] = h16_to_f32(b.y >> 16, p.f16);
+          bfull[8 * j + 4] = h16_to_f32(b.z & 0xFFFFu, p.f16);
+          bfull[8 * j + 5] = h16_to_f32(b.z >> 16, p.f16);
+          bfull[8 * j + 6] = h16_to_f32(b.w & 0xFFFFu, p.f16);
+          bfull[8 * j + 7] = h16_to_f32(b.w >> 16, p.f16);
         }
       } else {
 #pragma unroll
         for (int j = 0; j < 64; ++j)
-          bfull[j] = (row_ok && col0 + j < p.N) ? bf16_bits_to_f32(__ldg(brow + j)) : 0.f;
+          bfull[j] = (row_ok && col0 + j < p.N) ? h16_to_f32(__ldg(brow + j), p.f16) : 0.f;
       }
       if (!p.round_before_bias) {
 #pragma unroll
@@ -141,14 +151,14 @@ __device__ __forceinline__ void epilogue_chunk(const MatmulParams& p, const CUte
     }
     uint32_t packed[32];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+    for (int j = 0; j < 32; ++j) packed[j] = pack_h16x2(f[2 * j], f[2 * j + 1], p.f16);
     if (has_full && p.round_before_bias) {
       // 16-bit add after the downcast: bf16(float(bf16(acc)) + float(bias))
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        const float lo = bf16_bits_to_f32(packed[j] & 0xFFFFu) + bfull[2 * j];
-        const float hi = bf16_bits_to_f32(packed[j] >> 16) + bfull[2 * j + 1];
-        packed[j] = pack_bf16x2(lo, hi);
+        const float lo = h16_to_f32(packed[j] & 0xFFFFu, p.f16) + bfull[2 * j];
+        const float hi = h16_to_f32(packed[j] >> 16, p.f16) + bfull[2 * j + 1];
+        packed[j] = pack_h16x2(lo, hi, p.f16);
       }
     }
     // ---- staging buffer `buf` must no longer be read by the TMA store issued two chunks ago
@@ -176,7 +186,6 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
                            const __grid_constant__ CUtensorMap tmap_c, const MatmulParams p) {
   using L = MatmulSmem<BN, STAGES>;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
-  constexpr uint32_t IDESC = umma_idesc_bf16_f32(MM_BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -266,7 +275,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
           for (int k = 0; k < MM_BK / MM_UMMA_K; ++k) {
             const uint64_t a_desc = umma_smem_desc_sw128(a_addr + k * (MM_UMMA_K * 2), 16, 1024);
             const uint64_t b_desc = umma_smem_desc_sw128(b_addr + k * p.b_kstep, p.b_lbo, p.b_sbo);
-            umma_ss(d_tmem, a_desc, b_desc, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_ss(d_tmem, a_desc, b_desc, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // slot reusable once these MMAs have read it
           if (kb == p.num_kb - 1) umma_commit(&tmem_full_bar[acc]);  // accumulator complete
@@ -350,7 +359,6 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
                                 const __grid_constant__ CUtensorMap tmap_c, const MatmulParams p) {
   using L = Matmul2Smem<STAGES>;
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t IDESC = umma_idesc_bf16_f32(256, MM2_BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -452,7 +460,7 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
             for (int k = 0; k < MM_BK / MM_UMMA_K; ++k) {
               const uint64_t a_desc = umma_smem_desc_sw128(a_addr + k * (MM_UMMA_K * 2), 16, 1024);
               const uint64_t b_desc = umma_smem_desc_sw128(b_addr + k * (MM_UMMA_K * 128), MM_B_BOX_BYTES, 1024);
-              umma_ss_2cta(d_tmem, a_desc, b_desc, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+              umma_ss_2cta(d_tmem, a_desc, b_desc, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
             // release this ring slot in both CTAs once the MMAs above have read it
             const uint32_t e = smem_u32(&empty_bar[stage]);
@@ -554,6 +562,8 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
     if (sscanf(dbg, "%u,%u,%u", &l, &sb, &ks) == 3) { p.b_lbo = l; p.b_sbo = sb; p.b_kstep = ks; }
   }
   p.l2_hint = 0;
+  p.f16 = a.dtype;
+  p.idesc = umma_idesc_16bit_f32(MM_BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
   p.status = status;
 
   // per device (function attributes belong to the current context), cheap enough to repeat
@@ -590,6 +600,8 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   p.act = a.act;
   p.round_before_bias = a.round_before_bias;
   p.b_lbo = p.b_sbo = p.b_kstep = 0;  // fixed in the kernel
+  p.f16 = a.dtype;
+  p.idesc = umma_idesc_16bit_f32(256, MM2_BN, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
   p.l2_hint = 2;  // keep the group's A row panel in L2 (measured +2 % at 8192^3 over no hint; B evict_first loses)
   if (const char* h = getenv("B200K_MATMUL_L2_HINT")) p.l2_hint = atoi(h);
   p.status = status;
@@ -614,6 +626,7 @@ int matmul_bf16(const MatmulArgs& a, cudaStream_t stream, uint32_t* status_overr
   if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) | reinterpret_cast<uintptr_t>(a.C)) & 15u)
     return set_error(B200K_ERR_INVALID_ARG, "matmul: A, B and C must be 16-byte aligned");
   if (a.bias_kind < B200K_BIAS_NONE || a.bias_kind > B200K_BIAS_FULL_BF16) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad bias_kind %d", a.bias_kind);
+  if (a.dtype != 0 && a.dtype != 1) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad element type %d", a.dtype);
   if (a.act < B200K_ACT_NONE || a.act > B200K_ACT_LEAKY_RELU) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad act %d", a.act);
   if (a.bias_kind != B200K_BIAS_NONE && a.bias == nullptr) return set_error(B200K_ERR_INVALID_ARG, "matmul: bias_kind %d needs a bias pointer", a.bias_kind);
   if (a.bias_kind == B200K_BIAS_ROW_F32 && (reinterpret_cast<uintptr_t>(a.bias) & 15u))

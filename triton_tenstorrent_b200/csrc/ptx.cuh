@@ -163,6 +163,12 @@ __host__ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_
 //   bits [4,6) D format (1 = f32)   [7,10) A format (1 = bf16)   [10,13) B format (1 = bf16)
 //   bit 15 A major (1 = MN-major)   bit 16 B major (1 = MN-major)
 //   bits [17,23) N >> 3             bits [24,29) M >> 4
+// Same with fp16 inputs (A/B format 0) when is_f16 is set.
+__host__ __device__ constexpr uint32_t umma_idesc_16bit_f32(int m, int n, int a_mn_major, int b_mn_major, int is_f16) {
+  return (1u << 4) | ((is_f16 ? 0u : 1u) << 7) | ((is_f16 ? 0u : 1u) << 10) |
+         (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
 __host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int m, int n, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
          (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
@@ -345,6 +351,24 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+
+// fp16 counterparts of pack_bf16x2 / bf16_bits_to_f32
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t bits16) {
+  float f;
+  asm("{\n"
+      ".reg .b16 h;\n"
+      "cvt.u16.u32 h, %1;\n"
+      "cvt.f32.f16 %0, h;\n"
+      "}\n"
+      : "=f"(f)
+      : "r"(bits16));
+  return f;
+}
 
 // max(a, b, c) in one instruction
 __device__ __forceinline__ float fmax3(float a, float b, float c) {

@@ -29,12 +29,13 @@ launch_exit_hook = None
 
 
 class Kernel:
-    def __init__(self, name, arg_names, arg_types, meta_defaults, spec_keys=()):
+    def __init__(self, name, arg_names, arg_types, meta_defaults, spec_keys=(), spec_fn=None):
         self.name = name
         self.arg_names = tuple(arg_names)
         self.arg_types = dict(zip(arg_names, arg_types))
         self.meta_defaults = dict(meta_defaults)
         self.spec_keys = tuple(spec_keys)
+        self.spec_fn = spec_fn  # extra "KEY=VAL" items derived from the arguments (e.g. the element type)
         self.src = _driver.KernelSource(name=name, arg_names=self.arg_names,
                                         signature={i: self.arg_types[n] for i, n in enumerate(self.arg_names)})
         self.launcher = None
@@ -72,7 +73,10 @@ class Kernel:
         meta = {n: bound[n] for n in self.arg_names if self.arg_types[n] == "constexpr"}
         g = grid(meta) if callable(grid) else grid
         g = tuple(g) + (1,) * (3 - len(g))
-        spec = ",".join(f"{k}={int(bound[k])}" for k in self.spec_keys)
+        items = [f"{k}={int(bound[k])}" for k in self.spec_keys]
+        if self.spec_fn is not None:
+            items.extend(self.spec_fn(bound))
+        spec = ",".join(items)
         function = f"{self.name}:{spec}" if spec else self.name
         drv = _driver.active
         if self.launcher is None:
@@ -95,6 +99,11 @@ mul_add_kernel = Kernel(
     "mul_add_kernel", ["x_ptr", "y_ptr", "z_ptr", "output_ptr", "n_elements", "BLOCK_SIZE"],
     ["*fp32", "*fp32", "*fp32", "*fp32", "i32", "constexpr"], {}, spec_keys=("BLOCK_SIZE",))
 
+def _matmul_spec(bound):
+    """The compiled reference kernel is specialised on the descriptors' element type; here it travels in the name."""
+    return ["F16=1"] if bound["a_desc"].base.dtype == torch.float16 else []
+
+
 _MATMUL_META = {"BLOCK_SIZE_M": 128, "BLOCK_SIZE_N": 256, "BLOCK_SIZE_K": 64, "GROUP_SIZE_M": 8,
                 "FP8_OUTPUT": False, "WARP_SPECIALIZE": True}
 
@@ -102,13 +111,14 @@ matmul_kernel_tma = Kernel(
     "matmul_kernel_tma",
     ["a_desc", "b_desc", "c_desc", "M", "N", "K", "BLOCK_SIZE_M", "BLOCK_SIZE_N", "BLOCK_SIZE_K", "GROUP_SIZE_M",
      "FP8_OUTPUT", "WARP_SPECIALIZE"],
-    ["tensordesc", "tensordesc", "tensordesc", "i32", "i32", "i32"] + ["constexpr"] * 6, _MATMUL_META)
+    ["tensordesc", "tensordesc", "tensordesc", "i32", "i32", "i32"] + ["constexpr"] * 6, _MATMUL_META,
+    spec_fn=_matmul_spec)
 
 matmul_kernel_fused = Kernel(
     "matmul_kernel_fused",
     ["a_desc", "b_desc", "c_desc", "bias_desc", "M", "N", "K", "BLOCK_SIZE_M", "BLOCK_SIZE_N", "BLOCK_SIZE_K",
      "GROUP_SIZE_M", "FP8_OUTPUT", "WARP_SPECIALIZE"],
-    ["tensordesc"] * 4 + ["i32", "i32", "i32"] + ["constexpr"] * 6, _MATMUL_META)
+    ["tensordesc"] * 4 + ["i32", "i32", "i32"] + ["constexpr"] * 6, _MATMUL_META, spec_fn=_matmul_spec)
 
 _attn_fwd = Kernel(
     "_attn_fwd",

@@ -99,11 +99,11 @@ _ACTIVATIONS = {"": _lib.ACT_NONE, None: _lib.ACT_NONE, "none": _lib.ACT_NONE, "
 
 
 def _row_major_2d(t: torch.Tensor, name: str) -> torch.Tensor:
-    """A 2-D bf16 view the TMA path accepts: unit inner stride, 16-byte aligned rows and base."""
+    """A 2-D bf16 / fp16 view the TMA path accepts: unit inner stride, 16-byte aligned rows and base."""
     if t.dim() != 2:
         raise ValueError(f"{name}: 2-D tensor expected, got {t.dim()}-D")
-    if t.dtype != torch.bfloat16:
-        raise TypeError(f"{name}: bf16 expected, got {t.dtype}")
+    if t.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"{name}: bf16 or fp16 expected, got {t.dtype}")
     if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0 or t.stride(0) < t.shape[1]:
         if t.shape[1] % 8 != 0:
             raise ValueError(f"{name}: the row length must be a multiple of 8 elements (16-byte rows, the same "
@@ -121,12 +121,13 @@ def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT
     _, N = bd.shape
     if N % 8 != 0:
         raise ValueError(f"matmul: N must be a multiple of 8 (16-byte rows of C); got {N}")
+    dtype = ad.dtype
     if c is None:
-        c = torch.empty((M, N), device=ad.device, dtype=torch.bfloat16)
-    elif (tuple(c.shape) != (M, N) or c.dtype != torch.bfloat16 or not c.is_cuda or c.device != ad.device
+        c = torch.empty((M, N), device=ad.device, dtype=dtype)
+    elif (tuple(c.shape) != (M, N) or c.dtype != dtype or not c.is_cuda or c.device != ad.device
           or c.stride(1) != 1 or c.stride(0) % 8 != 0 or c.data_ptr() % 16 != 0):
-        raise ValueError(f"matmul: the output must be a bf16 [{M},{N}] tensor on {ad.device} with unit inner stride "
-                         "and 16-byte aligned rows")
+        raise ValueError(f"matmul: the output must be a {dtype} [{M},{N}] tensor on {ad.device} with unit inner "
+                         "stride and 16-byte aligned rows")
     bias_ptr, ldbias = 0, 0
     if bias_kind == _lib.BIAS_ROW_F32:
         bias = _to_device(bias).contiguous()
@@ -136,20 +137,21 @@ def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT
     elif bias_kind == _lib.BIAS_FULL_BF16:
         bias = _to_device(bias)
         assert bias.shape == (M, N), "Incompatible bias dimensions"
-        if bias.dtype != torch.bfloat16:
-            raise TypeError(f"bias must be bf16 [M,N], got {bias.dtype}")
+        if bias.dtype != dtype:
+            raise TypeError(f"bias must be {dtype} [M,N] like the operands, got {bias.dtype}")
         if bias.stride(1) != 1:
             bias = bias.contiguous()
         bias_ptr, ldbias = bias.data_ptr(), bias.stride(0)
+    entry = lib.b200k_matmul_f16 if dtype == torch.float16 else lib.b200k_matmul_bf16
     with torch.cuda.device(ad.device):
-        _lib.check(lib.b200k_matmul_bf16(ad.data_ptr(), bd.data_ptr(), c.data_ptr(), M, N, K, ad.stride(0), bd.stride(0),
-                                         c.stride(0), bias_ptr, bias_kind, ldbias, act, round_before_bias, _stream()))
+        _lib.check(entry(ad.data_ptr(), bd.data_ptr(), c.data_ptr(), M, N, K, ad.stride(0), bd.stride(0),
+                         c.stride(0), bias_ptr, bias_kind, ldbias, act, round_before_bias, _stream()))
     return c
 
 
 def matmul_tma(a: torch.Tensor, b: torch.Tensor, warp_specialize: bool = True, out: torch.Tensor = None) -> torch.Tensor:
-    """C = A.B, bf16 in/out, fp32 accumulate.  Mirrors matmul_tma(a, b, warp_specialize),
-    examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py:146-173.  `warp_specialize` is accepted for
+    """C = A.B, bf16 (or fp16) in/out, fp32 accumulate.  Mirrors matmul_tma(a, b, warp_specialize),
+    examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py:146-173 (fp16 twin: 09-persistent-matmul.py:148-175).  `warp_specialize` is accepted for
     surface compatibility; the kernel is always warp-specialised."""
     return _like_input(_matmul_call(a, b, c=out if (out is not None and out.is_cuda) else None), a, out)
 
