@@ -392,6 +392,23 @@ def test_host_tensor_round_trip():
     assert not c.is_cuda and oracle.rel_frobenius(c.float(), oracle.golden_matmul(a, b).float()) <= MATMUL_REL_FRO
 
 
+def test_host_tensor_pipeline_matches_device_path():
+    # large host operands go through the row-block pipeline (upload / multiply / download overlapped);
+    # the result must be bit-identical to the plain device path
+    M, N, K = 4096 + 384, 1288, 520                      # ragged last block, N and K tails
+    a, b = gi.matmul_inputs(M, N, K, seed=41)
+    bias = gi.row_bias(N)
+    ref = ops.matmul_tma(a.cuda(), b.cuda(), True).cpu()
+    got = ops.matmul_tma(a.pin_memory(), b.pin_memory(), True)
+    assert not got.is_cuda and torch.equal(got.view(torch.int16), ref.view(torch.int16))
+    got2 = ops.matmul_tma(a, b, True, out=torch.empty((M, N), dtype=torch.bfloat16).pin_memory())   # pageable inputs
+    assert torch.equal(got2.view(torch.int16), ref.view(torch.int16))
+    reff = ops.matmul_fused(a.cuda(), b.cuda(), bias.cuda(), "relu").cpu()
+    gotf = ops.matmul_fused(a, b, bias, "relu")
+    assert torch.equal(gotf.view(torch.int16), reff.view(torch.int16))
+    assert oracle.rel_frobenius(got[:64].float(), oracle.golden_matmul(a[:64], b).float()) <= MATMUL_REL_FRO
+
+
 def test_launch_counter_counts_kernels():
     lib = _lib.load()
     before = lib.b200k_launch_count()

@@ -112,6 +112,62 @@ def _row_major_2d(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
+_HOST_CHUNK_ROWS = 1024     # rows of A / C per piece of the host-tensor pipeline (a multiple of the 256-row tile)
+_copy_streams = {}
+
+
+def _side_streams(device):
+    """Two extra streams per device: host-to-device and device-to-host copies of the host-tensor pipeline."""
+    key = torch.device(device).index
+    if key not in _copy_streams:
+        _copy_streams[key] = (torch.cuda.Stream(device=device), torch.cuda.Stream(device=device))
+    return _copy_streams[key]
+
+
+def _matmul_host_streamed(a, b, out, bias, bias_kind, act, round_before_bias):
+    """C = epilogue(A.B) for HOST operands, as a three-stage pipeline over row blocks of A and C:
+    while block i is multiplied, block i+1 of A travels to the device and block i-1 of C travels back
+    (PCIe is full duplex), so a call costs about the upload of B plus the upload of A instead of the
+    sum of all copies and the kernel.  Pinned host tensors make the copies asynchronous; pageable ones
+    still work (torch stages them).  Returns a host tensor (`out` if given)."""
+    _require_cuda()
+    device = torch.device("cuda", torch.cuda.current_device())
+    M, K = a.shape
+    N = b.shape[1]
+    main = torch.cuda.current_stream(device)
+    s_in, s_out = _side_streams(device)
+    if out is None:
+        out = torch.empty((M, N), dtype=a.dtype, pin_memory=True)
+    elif tuple(out.shape) != (M, N) or out.dtype != a.dtype or out.is_cuda:
+        raise ValueError(f"out must be a host {a.dtype} [{M},{N}] tensor")
+    a_dev = torch.empty((M, K), dtype=a.dtype, device=device)
+    c_dev = torch.empty((M, N), dtype=a.dtype, device=device)
+    s_in.wait_stream(main)
+    s_out.wait_stream(main)
+    with torch.cuda.stream(s_in):
+        b_dev = b.to(device, non_blocking=True)
+        bias_dev = bias.to(device, non_blocking=True) if bias is not None else None
+    blocks = [(r, min(r + _HOST_CHUNK_ROWS, M)) for r in range(0, M, _HOST_CHUNK_ROWS)]
+    for (r0, r1) in blocks:
+        with torch.cuda.stream(s_in):
+            a_dev[r0:r1].copy_(a[r0:r1], non_blocking=True)
+            ready = s_in.record_event()
+        main.wait_event(ready)
+        _matmul_call(a_dev[r0:r1], b_dev, c=c_dev[r0:r1],
+                     bias=(bias_dev[r0:r1] if bias_kind == _lib.BIAS_FULL_BF16 else bias_dev),
+                     bias_kind=bias_kind, act=act, round_before_bias=round_before_bias)
+        done = main.record_event()
+        s_out.wait_event(done)
+        with torch.cuda.stream(s_out):
+            out[r0:r1].copy_(c_dev[r0:r1], non_blocking=True)
+    main.wait_stream(s_out)
+    s_out.synchronize()
+    for t in (a_dev, c_dev, b_dev):      # the side streams used these allocations
+        t.record_stream(s_in)
+        t.record_stream(s_out)
+    return out
+
+
 def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT_NONE, round_before_bias=0):
     assert a.shape[1] == b.shape[0], "Incompatible dimensions"
     assert a.dtype == b.dtype, "Incompatible dtypes"
@@ -153,7 +209,17 @@ def matmul_tma(a: torch.Tensor, b: torch.Tensor, warp_specialize: bool = True, o
     """C = A.B, bf16 (or fp16) in/out, fp32 accumulate.  Mirrors matmul_tma(a, b, warp_specialize),
     examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py:146-173 (fp16 twin: 09-persistent-matmul.py:148-175).  `warp_specialize` is accepted for
     surface compatibility; the kernel is always warp-specialised."""
+    if _host_pipeline_applies(a, b, out):
+        return _matmul_host_streamed(a, b, out, None, _lib.BIAS_NONE, _lib.ACT_NONE, 0)
     return _like_input(_matmul_call(a, b, c=out if (out is not None and out.is_cuda) else None), a, out)
+
+
+def _host_pipeline_applies(a, b, out, bias=None) -> bool:
+    """Host operands, a host (or no) output, and enough rows for at least two pieces."""
+    return (not a.is_cuda and not b.is_cuda and (out is None or not out.is_cuda) and (bias is None or not bias.is_cuda)
+            and a.dim() == 2 and b.dim() == 2 and a.is_contiguous() and b.is_contiguous()
+            and a.shape[0] >= 2 * _HOST_CHUNK_ROWS and a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0
+            and a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16))
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "") -> torch.Tensor:
@@ -172,6 +238,8 @@ def matmul_fused(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor, activatio
     This is the [N]-bias + ReLU epilogue of the fused-matmul workload."""
     if activation not in _ACTIVATIONS:
         raise ValueError(f"unknown activation {activation!r}")
+    if _host_pipeline_applies(a, b, out, bias) and bias.dtype == torch.float32 and tuple(bias.shape) == (b.shape[1],):
+        return _matmul_host_streamed(a, b, out, bias, _lib.BIAS_ROW_F32, _ACTIVATIONS[activation], 0)
     return _like_input(_matmul_call(a, b, c=out if (out is not None and out.is_cuda) else None, bias=bias,
                                     bias_kind=_lib.BIAS_ROW_F32, act=_ACTIVATIONS[activation]), a, out)
 
