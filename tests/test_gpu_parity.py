@@ -282,7 +282,7 @@ def test_matmul_rejects_bad_arguments():
 
 
 # ------------------------------------------------------------------------------------------------ attention
-@pytest.mark.parametrize("case", [c for c in gi.ATTN_CASES if c[3] == 128])
+@pytest.mark.parametrize("case", gi.ATTN_CASES)
 def test_attention_golden(golden_dir, case):
     Z, H, S, D, causal, BM, BN = case
     g = np.load(golden_dir / "attention.npz")
@@ -338,9 +338,19 @@ def test_attention_rejects_unsupported():
     q = torch.zeros(1, 1, 100, 128, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(NotImplementedError):
         ops.attention(q, q, q, False, 0.1)
-    q64 = torch.zeros(1, 1, 128, 64, dtype=torch.bfloat16, device="cuda")
+    q32 = torch.zeros(1, 1, 128, 32, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(NotImplementedError):
-        ops.attention(q64, q64, q64, False, 0.1)
+        ops.attention(q32, q32, q32, False, 0.1)
+
+
+@pytest.mark.parametrize("Z,H,S,causal", [(1, 2, 128, True), (2, 3, 512, False), (1, 4, 1024, True), (1, 1, 384, False)])
+def test_attention_head_dim_64(Z, H, S, causal):
+    D = 64
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=24)
+    ref_o, ref_m = oracle.attention(q, k, v, causal, D ** -0.5, BLOCK_M=128, BLOCK_N=64)   # BLOCK_N <= HEAD_DIM
+    o, m = ops.attention_with_lse(q.cuda(), k.cuda(), v.cuda(), causal, D ** -0.5)
+    assert float((o.cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
+    assert float((m.cpu() - ref_m).abs().max()) <= 1e-4
 
 
 # ------------------------------------------------------------------------------------------------ launch surface

@@ -1,5 +1,5 @@
 // Fused attention forward for sm_100a: O = softmax(Q K^T * sm_scale [+ causal mask]) V, bf16 in/out,
-// HEAD_DIM 128, blockwise online softmax in the base-2 domain exactly like the reference kernel
+// HEAD_DIM 64 or 128, blockwise online softmax in the base-2 domain exactly like the reference kernel
 // (examples/fused-attn/06-fused-attention.py:33-90 inner loop, :143-215 prologue/epilogue).
 //
 // One CTA owns a pair of adjacent 128-row Q tiles of one (batch, head) and walks the K/V blocks of
@@ -33,17 +33,23 @@ namespace b200k {
 
 constexpr int AT_BM = 128;            // rows per Q tile
 constexpr int AT_BN = 128;            // keys per K/V block
-constexpr int AT_D = 128;             // head dimension
+constexpr int AT_D_MAX = 128;         // head dimensions 64 and 128 are built
 constexpr int AT_THREADS = 384;         // three warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
-constexpr int AT_TILE_BYTES = AT_BM * AT_D * 2;  // 32 KB: two 16 KB boxes of 64 columns
-constexpr int AT_BOX_BYTES = 16384;
+constexpr int AT_BOX_BYTES = 16384;   // one TMA box: 128 rows x 64 columns of bf16
 constexpr int AT_NSLOT = 5;           // K/V ring slots
-constexpr int AT_Q_OFF = 0;
-constexpr int AT_KV_OFF = 2 * AT_TILE_BYTES;
-constexpr int AT_BAR_OFF = AT_KV_OFF + AT_NSLOT * AT_TILE_BYTES;
 constexpr int AT_NBAR = 2 + 2 + 2 * AT_NSLOT + 2 + 2 + 2;
-constexpr int AT_SMEM_TOTAL = AT_BAR_OFF + AT_NBAR * 8 + 16 + 1024;
-static_assert(AT_SMEM_TOTAL <= 232448, "attention shared memory budget exceeded");
+// Shared-memory layout for head dimension D: Q0 | Q1 | K/V ring | barriers.  A 128 x D tile is D/64 boxes.
+template <int D>
+struct AttnCfg {
+  static_assert(D == 64 || D == 128, "head dimension");
+  static constexpr int NBOX = D / 64;
+  static constexpr int TILE_BYTES = NBOX * AT_BOX_BYTES;   // 16 KB or 32 KB
+  static constexpr int Q_OFF = 0;
+  static constexpr int KV_OFF = 2 * TILE_BYTES;
+  static constexpr int BAR_OFF = KV_OFF + AT_NSLOT * TILE_BYTES;
+  static constexpr int SMEM_TOTAL = BAR_OFF + AT_NBAR * 8 + 16 + 1024;
+  static_assert(SMEM_TOTAL <= 232448, "attention shared memory budget exceeded");
+};
 
 constexpr float AT_RESCALE_THRESHOLD = 8.0f;  // log2 units
 
@@ -91,18 +97,21 @@ __device__ __forceinline__ float ex2_approx(float x) {
 constexpr int AT_REGS_SOFTMAX = 216;
 constexpr int AT_REGS_OTHER = 72;
 
+template <int D>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
                              const AttnParams p) {
   constexpr uint32_t IDESC_S = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);   // Q (K-major) x K^T (K-major)
-  constexpr uint32_t IDESC_PV = umma_idesc_bf16_f32(AT_BM, AT_D, 0, 1);   // P (TMEM) x V (N-major)
+  constexpr uint32_t IDESC_PV = umma_idesc_bf16_f32(AT_BM, D, 0, 1);      // P (TMEM) x V (N-major)
+  using Cfg = AttnCfg<D>;
+  constexpr int AT_TILE_BYTES = Cfg::TILE_BYTES;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_q = smem + AT_Q_OFF;
-  uint8_t* smem_kv = smem + AT_KV_OFF;
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + AT_BAR_OFF);
+  uint8_t* smem_q = smem + Cfg::Q_OFF;
+  uint8_t* smem_kv = smem + Cfg::KV_OFF;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
   uint64_t* q_empty = q_full + 2;
   uint64_t* kv_full = q_empty + 2;
   uint64_t* kv_empty = kv_full + AT_NSLOT;
@@ -165,8 +174,9 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           if (lane == 0) {
             mbar_expect_tx(&q_full[t], AT_TILE_BYTES);
             const int row = row_base + it.mblk[t] * AT_BM;
-            tma_load_2d(smem_q + t * AT_TILE_BYTES, &tmap_q, &q_full[t], 0, row);
-            tma_load_2d(smem_q + t * AT_TILE_BYTES + AT_BOX_BYTES, &tmap_q, &q_full[t], 64, row);
+#pragma unroll
+            for (int bx = 0; bx < Cfg::NBOX; ++bx)
+              tma_load_2d(smem_q + t * AT_TILE_BYTES + bx * AT_BOX_BYTES, &tmap_q, &q_full[t], bx * 64, row);
           }
           __syncwarp();
           ++q_loads[t];
@@ -180,8 +190,8 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           const CUtensorMap* tm = is_v ? &tmap_v : &tmap_k;
           const int row = row_base + j * AT_BN;
           uint8_t* dst = smem_kv + slot * AT_TILE_BYTES;
-          tma_load_2d(dst, tm, &kv_full[slot], 0, row);
-          tma_load_2d(dst + AT_BOX_BYTES, tm, &kv_full[slot], 64, row);
+#pragma unroll
+          for (int bx = 0; bx < Cfg::NBOX; ++bx) tma_load_2d(dst + bx * AT_BOX_BYTES, tm, &kv_full[slot], bx * 64, row);
         }
         __syncwarp();
         if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
@@ -201,7 +211,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       // S_t = Q_t K^T : 8 MMAs of K = 16 over the head dimension (two 64-column boxes)
       if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < AT_D / 16; ++k) {
+        for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * AT_BOX_BYTES + (k & 3) * 32;
           umma_ss(tmem_base + t * 128, umma_smem_desc_sw128(q_addr[t] + off, 16, 1024),
                   umma_smem_desc_sw128(k_addr + off, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
@@ -349,7 +359,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           if (j > 0) {
             // the PV MMA of block j-1 has completed (its completion precedes s_full of block j)
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c4 = 0; c4 < D / 32; ++c4) {
               uint32_t o[32];
               tmem_ld_x32(t_o + c4 * 32, o);
               tmem_wait_ld();
@@ -413,7 +423,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       tc_fence_after();
       const float inv_l = 1.0f / l;
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
+      for (int c4 = 0; c4 < D / 32; ++c4) {
         uint32_t o[32];
         tmem_ld_x32(t_o + c4 * 32, o);
         tmem_wait_ld();
@@ -436,8 +446,8 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       __syncwarp();
       if (lane == 0) {
         const int y = static_cast<int>(out_row) + q * 32;
-        tma_store_2d(&tmap_o, stage + q * 32 * 128, 0, y);
-        tma_store_2d(&tmap_o, stage + AT_BOX_BYTES + q * 32 * 128, 64, y);
+#pragma unroll
+        for (int bx = 0; bx < Cfg::NBOX; ++bx) tma_store_2d(&tmap_o, stage + bx * AT_BOX_BYTES + q * 32 * 128, bx * 64, y);
         tma_store_commit();
         tma_store_wait_read<0>();
         mbar_arrive(&q_empty[t]);  // the Q buffer may be refilled
@@ -457,7 +467,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
   }
 }
 
-int attn_supported(int D, int N_CTX) { return (D == AT_D && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0; }
+int attn_supported(int D, int N_CTX) { return ((D == 64 || D == 128) && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0; }
 
 static int pick_grid(int sm_count, int num_items, int num_pairs, bool causal) {
   int grid = num_items < sm_count ? num_items : sm_count;
@@ -474,7 +484,7 @@ static int pick_grid(int sm_count, int num_items, int num_pairs, bool causal) {
 static int attn_check_args(const AttnArgs& a) {
   if (a.Z <= 0 || a.H <= 0 || a.N_CTX <= 0) return set_error(B200K_ERR_INVALID_ARG, "attention: Z, H, N_CTX must be positive");
   if (!attn_supported(a.D, a.N_CTX))
-    return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 128, N_CTX multiple of 128)", a.D, a.N_CTX);
+    return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 64 or 128, N_CTX multiple of 128)", a.D, a.N_CTX);
   if (a.q == nullptr || a.k == nullptr || a.v == nullptr || a.o == nullptr || a.lse2 == nullptr)
     return set_error(B200K_ERR_INVALID_ARG, "attention: null pointer");
   if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
@@ -491,10 +501,11 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
   const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
   CUtensorMap tq, tk, tv, to;
   int rc;
-  if ((rc = make_tmap_bf16_2d(&tq, a.q, AT_D, rows, AT_D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tk, a.k, AT_D, rows, AT_D, 64, AT_BN)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tv, a.v, AT_D, rows, AT_D, 64, AT_BN)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&to, a.o, AT_D, rows, AT_D, 64, 32)) != 0) return rc;
+  const uint64_t D = static_cast<uint64_t>(a.D);
+  if ((rc = make_tmap_bf16_2d(&tq, a.q, D, rows, D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tk, a.k, D, rows, D, 64, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tv, a.v, D, rows, D, 64, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&to, a.o, D, rows, D, 64, 32)) != 0) return rc;
 
   AttnParams p;
   p.ZH = a.Z * a.H;
@@ -507,12 +518,18 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
   p.lse2 = a.lse2;
   p.status = status;
 
-  // per device (function attributes belong to the current context), cheap enough to repeat
-  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        AT_SMEM_TOTAL));
   int grid = pick_grid(sm_count, p.num_items, p.num_pairs, p.causal != 0);
   if (const char* g = getenv("B200K_ATTN_GRID")) { int v = atoi(g); if (v > 0 && v <= p.num_items) grid = v; }
-  attn_fwd_bf16_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_TOTAL, stream>>>(tq, tk, tv, to, p);
+  // function attributes belong to the current context (per device); cheap enough to repeat
+  if (a.D == 64) {
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          AttnCfg<64>::SMEM_TOTAL));
+    attn_fwd_bf16_tcgen05_kernel<64><<<grid, AT_THREADS, AttnCfg<64>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, p);
+  } else {
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          AttnCfg<128>::SMEM_TOTAL));
+    attn_fwd_bf16_tcgen05_kernel<128><<<grid, AT_THREADS, AttnCfg<128>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, p);
+  }
   count_launch();
   B200K_CHECK_LAUNCH("attn_fwd_bf16_tcgen05_kernel");
   return B200K_OK;
