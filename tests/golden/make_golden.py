@@ -1,7 +1,7 @@
 """Generates the golden vectors under tests/golden/ by EXECUTING the reference's own kernel sources.
 
 The reference's kernels are Triton `@triton.jit` functions.  This script reads them from a checkout
-of kernelize-ai/triton-tenstorrent (default: /root/reference, override with REFERENCE_ROOT), extracts
+of kernelize-ai/triton-tenstorrent (its path is taken from the REFERENCE_ROOT environment variable), extracts
 the kernel functions by name with `ast` (several example files cannot be imported as a whole: they
 query an active Triton driver or launch on a device at import time), writes them to a temporary
 module and runs them on CPU tensors with Triton's interpreter (TRITON_INTERPRET=1, triton 3.6).
@@ -21,7 +21,7 @@ Outputs (small .npz files, a few hundred KB in total):
 Inputs are regenerated from their seeds by `golden_inputs.py`; each .npz keeps a sha256 of the
 input bytes so that a drift of torch's CPU RNG cannot silently invalidate the vectors.
 
-Run:  python tests/golden/make_golden.py
+Run:  REFERENCE_ROOT=<checkout of the reference> python tests/golden/make_golden.py
 """
 from __future__ import annotations
 
@@ -41,7 +41,9 @@ HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
 import golden_inputs as gi  # noqa: E402
 
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+if "REFERENCE_ROOT" not in os.environ:
+    raise SystemExit("set REFERENCE_ROOT to a checkout of kernelize-ai/triton-tenstorrent")
+REF = Path(os.environ["REFERENCE_ROOT"])
 
 KERNEL_SOURCES = {
     # module name -> (reference file, functions to extract in order)
