@@ -182,6 +182,15 @@ int b200k_block_range(int64_t num_blocks, int workers, int w, int64_t* block_sta
  */
 int b200k_device_status(void* stream, uint32_t* code);
 
+/*
+ * Failure-detection self-test: launches a one-warp kernel whose only wait can never be satisfied and
+ * has a budget of `budget_cycles` SM cycles (a few million = about a millisecond).  The wait gives up,
+ * the kernel returns normally, and the next b200k_device_status reports B200K_ERR_DEVICE_TIMEOUT with
+ * site 99.  Exercises, without faulting or hanging anything, the same bounded-wait code the matmul and
+ * attention kernels use.  No counterpart in the reference (its launches have no device-side waits).
+ */
+int b200k_selftest_wait_timeout(int64_t budget_cycles, void* stream);
+
 /* Number of kernel launches issued by this library in the calling process (all threads). */
 int64_t b200k_launch_count(void);
 

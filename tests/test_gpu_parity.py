@@ -419,6 +419,25 @@ def test_host_tensor_pipeline_matches_device_path():
     assert oracle.rel_frobenius(got[:64].float(), oracle.golden_matmul(a[:64], b).float()) <= MATMUL_REL_FRO
 
 
+def test_bounded_wait_gives_up_and_context_survives():
+    # a wait that can never be satisfied runs out of its (tiny) budget: status word set, kernel returns,
+    # and the device keeps working
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    assert ops.device_status() == 0
+    _lib.check(lib.b200k_selftest_wait_timeout(2_000_000, stream))       # about a millisecond
+    code = ctypes.c_uint32(0)
+    rc = lib.b200k_device_status(stream, ctypes.byref(code))
+    assert rc == _lib.ERR_DEVICE_TIMEOUT and code.value >> 8 == 99 and "site 99" in _lib.last_error()
+    assert ops.device_status() == 0                                      # reading the status cleared it
+    x, y = gi.add_inputs(4096)
+    assert _bits_equal(ops.add(x.cuda(), y.cuda()).cpu(), oracle.add(x, y))
+    a, b = gi.matmul_inputs(256, 256, 256)
+    assert oracle.rel_frobenius(ops.matmul_tma(a.cuda(), b.cuda()).cpu().float(), oracle.golden_matmul(a, b).float()) <= MATMUL_REL_FRO
+    with pytest.raises(_lib.B200KError):
+        _lib.check(lib.b200k_selftest_wait_timeout(0, stream))
+
+
 def test_launch_counter_counts_kernels():
     lib = _lib.load()
     before = lib.b200k_launch_count()

@@ -406,6 +406,11 @@ int b200k_device_status(void* stream, uint32_t* code) {
   return B200K_OK;
 }
 
+int b200k_selftest_wait_timeout(int64_t budget_cycles, void* stream) {
+  clear_error();
+  return selftest_wait_timeout(budget_cycles, static_cast<cudaStream_t>(stream));
+}
+
 int64_t b200k_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

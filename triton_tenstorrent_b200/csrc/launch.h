@@ -77,5 +77,6 @@ struct AttnArgs {
 };
 int attn_fwd_bf16(const AttnArgs& a, cudaStream_t s);
 int attn_supported(int D, int N_CTX);
+int selftest_wait_timeout(long long budget_cycles, cudaStream_t s);
 
 }  // namespace b200k

@@ -62,6 +62,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 struct WaitCtx {
   volatile uint32_t* abort_flag;  // shared memory; non-zero => someone gave up, everybody unwinds
   uint32_t* status;               // global memory; first failure code wins
+  long long budget = B200K_WAIT_CYCLES;  // cycles one wait may take
 };
 
 // Waits for the phase with the given parity to complete.  Returns false when the CTA is aborting
@@ -75,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
       if (*ctx.abort_flag != 0) return false;
-      if (clock64() - t0 > B200K_WAIT_CYCLES) {
+      if (clock64() - t0 > ctx.budget) {
         *ctx.abort_flag = 1;
         if (ctx.status != nullptr) atomicCAS(ctx.status, 0u, (site << 8) | 1u);
         return false;
