@@ -89,6 +89,26 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// In place: s[i] <- exp2(s[i] * scale - m) for 32 scores (fp32 bits), adding the results to two pair sums.
+// Pass 1: 16 packed multiply-subtracts; pass 2: 32 exponentials; pass 3: 16 packed adds.
+__device__ __forceinline__ void exp_block32(uint32_t (&s)[32], uint64_t scale2, uint64_t negm2, uint64_t& sum_a,
+                                            uint64_t& sum_b) {
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    float x0, x1;
+    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, negm2), x0, x1);
+    s[2 * c] = __float_as_uint(x0);
+    s[2 * c + 1] = __float_as_uint(x1);
+  }
+#pragma unroll
+  for (int c = 0; c < 32; ++c) s[c] = __float_as_uint(ex2_approx(__uint_as_float(s[c])));
+#pragma unroll
+  for (int c = 0; c < 16; c += 2) {
+    sum_a = add_f32x2(sum_a, pack_f32x2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])));
+    sum_b = add_f32x2(sum_b, pack_f32x2(__uint_as_float(s[2 * c + 2]), __uint_as_float(s[2 * c + 3])));
+  }
+}
+
 // 12 warps start with 168 registers each (16384 per scheduler partition / 96 threads).  The third
 // warpgroup then returns registers to the CTA's pool and the softmax warpgroups take them
 // (setmaxnreg), so that a softmax thread can hold a whole row of scores plus the packed P values
@@ -374,33 +394,27 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         const uint64_t scale2 = pack_f32x2(scale, scale);
         const uint64_t negm2 = pack_f32x2(-m_used, -m_used);
         uint64_t sum_a = 0, sum_b = 0;  // bit pattern of (0.f, 0.f)
+        // Three passes per 32 scores, each over independent registers, so that the latency of the
+        // special-function unit is covered by the other exponentials instead of by stalls.
+        exp_block32(s0, scale2, negm2, sum_a, sum_b);
+        exp_block32(s1, scale2, negm2, sum_a, sum_b);
         {
           uint32_t pk[32];
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
-            float a0, a1, b0, b1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1])), scale2, negm2), a0, a1);
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s1[2 * c]), __uint_as_float(s1[2 * c + 1])), scale2, negm2), b0, b1);
-            a0 = ex2_approx(a0); a1 = ex2_approx(a1); b0 = ex2_approx(b0); b1 = ex2_approx(b1);
-            sum_a = add_f32x2(sum_a, pack_f32x2(a0, a1));
-            sum_b = add_f32x2(sum_b, pack_f32x2(b0, b1));
-            pk[c] = pack_bf16x2(a0, a1);
-            pk[16 + c] = pack_bf16x2(b0, b1);
+            pk[c] = pack_bf16x2(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1]));
+            pk[16 + c] = pack_bf16x2(__uint_as_float(s1[2 * c]), __uint_as_float(s1[2 * c + 1]));
           }
           tmem_st_x32(t_s, pk);
         }
+        exp_block32(s2, scale2, negm2, sum_a, sum_b);
+        exp_block32(s3, scale2, negm2, sum_a, sum_b);
         {
           uint32_t pk[32];
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
-            float a0, a1, b0, b1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s2[2 * c]), __uint_as_float(s2[2 * c + 1])), scale2, negm2), a0, a1);
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s3[2 * c]), __uint_as_float(s3[2 * c + 1])), scale2, negm2), b0, b1);
-            a0 = ex2_approx(a0); a1 = ex2_approx(a1); b0 = ex2_approx(b0); b1 = ex2_approx(b1);
-            sum_a = add_f32x2(sum_a, pack_f32x2(a0, a1));
-            sum_b = add_f32x2(sum_b, pack_f32x2(b0, b1));
-            pk[c] = pack_bf16x2(a0, a1);
-            pk[16 + c] = pack_bf16x2(b0, b1);
+            pk[c] = pack_bf16x2(__uint_as_float(s2[2 * c]), __uint_as_float(s2[2 * c + 1]));
+            pk[16 + c] = pack_bf16x2(__uint_as_float(s3[2 * c]), __uint_as_float(s3[2 * c + 1]));
           }
           tmem_st_x32(t_s + 32, pk);
         }
