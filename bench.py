@@ -259,7 +259,8 @@ def main():
     peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"{'sustained' if sustained else 'burst'} cuBLAS bf16, {peaks['source']}",
-                "frac_of_burst": achieved / peaks["bf16_tflops"], "frac_of_nominal_2250": achieved / 2250.0,
+                "frac_of_burst": achieved / peaks["bf16_tflops"],
+                "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"], "frac_of_nominal_2250": achieved / 2250.0,
                 "kernel": "matmul_bf16_tcgen05_2cta_kernel<6>", "kernel_ms": kernel_ms}
 
     # ---- end to end through the public wrapper with pinned host buffers
