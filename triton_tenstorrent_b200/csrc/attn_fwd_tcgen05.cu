@@ -227,27 +227,33 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     const uint32_t q_addr[2] = {smem_u32(smem_q), smem_u32(smem_q + AT_TILE_BYTES)};
     const uint32_t kv_addr0 = smem_u32(smem_kv);
 
-    auto issue_s = [&](int t, uint32_t k_addr) {
-      // S_t = Q_t K^T : 8 MMAs of K = 16 over the head dimension (two 64-column boxes)
+    // Descriptors differ from one MMA to the next only in the start-address field (bits 0..13, in
+    // units of 16 bytes): build one per operand base and add the offset, so that issuing an MMA
+    // costs a couple of integer instructions and the issue thread stays ahead of the tensor pipe.
+    const uint64_t q_desc[2] = {umma_smem_desc_sw128(q_addr[0], 16, 1024), umma_smem_desc_sw128(q_addr[1], 16, 1024)};
+    const uint64_t k_desc0 = umma_smem_desc_sw128(kv_addr0, 16, 1024);            // K block: K-major
+    const uint64_t v_desc0 = umma_smem_desc_sw128(kv_addr0, AT_BOX_BYTES, 1024);  // V block: N-major
+    auto issue_s = [&](int t, int slot_idx) {
+      // S_t = Q_t K^T : D/16 MMAs of K = 16 over the head dimension (64-column boxes)
       if (lane == 0) {
+        const uint64_t kd = k_desc0 + static_cast<uint64_t>((slot_idx * AT_TILE_BYTES) >> 4);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * AT_BOX_BYTES + (k & 3) * 32;
-          umma_ss(tmem_base + t * 128, umma_smem_desc_sw128(q_addr[t] + off, 16, 1024),
-                  umma_smem_desc_sw128(k_addr + off, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>(((k >> 2) * AT_BOX_BYTES + (k & 3) * 32) >> 4);
+          umma_ss(tmem_base + t * 128, q_desc[t] + off, kd + off, IDESC_S, k > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[t]);
       }
       __syncwarp();
     };
-    auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
+    auto issue_pv = [&](int t, int slot_idx, bool accumulate) {
       // O_t (+)= P_t V : 8 MMAs of K = 16 over the keys; P_t is bf16 in TMEM (8 columns per K step)
       if (lane == 0) {
+        const uint64_t vd = v_desc0 + static_cast<uint64_t>((slot_idx * AT_TILE_BYTES) >> 4);
 #pragma unroll
         for (int k = 0; k < AT_BN / 16; ++k)
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
-                  umma_smem_desc_sw128(v_addr + k * 2048, AT_BOX_BYTES, 1024), IDESC_PV,
-                  (accumulate || k > 0) ? 1u : 0u);
+          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, vd + static_cast<uint64_t>((k * 2048) >> 4),
+                  IDESC_PV, (accumulate || k > 0) ? 1u : 0u);
       }
       __syncwarp();
     };
@@ -257,7 +263,6 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       // ---- block 0 scores
       ok = mbar_wait(&kv_full[slot], slot_phase, ctx, 20);
       if (!ok) break;
-      uint32_t k_addr = kv_addr0 + slot * AT_TILE_BYTES;
       int k_slot = slot;
       if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
       for (int t = 0; ok && t < 2; ++t) {
@@ -266,7 +271,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         if (!ok) break;
         ++q_cnt[t];
         tc_fence_after();
-        issue_s(t, k_addr);
+        issue_s(t, k_slot);
       }
       if (!ok) break;
       if (lane == 0) umma_commit(&kv_empty[k_slot]);
@@ -275,7 +280,6 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       for (int j = 0; ok && j < it.n; ++j) {
         ok = mbar_wait(&kv_full[slot], slot_phase, ctx, 22);  // V_j
         if (!ok) break;
-        const uint32_t v_addr = kv_addr0 + slot * AT_TILE_BYTES;
         const int v_slot = slot;
         if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
         const bool have_next = (j + 1 < it.n);
@@ -286,7 +290,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
             if (!ok) break;
             ++p_cnt[t];
             tc_fence_after();
-            issue_pv(t, v_addr, j > 0);
+            issue_pv(t, v_slot, j > 0);
             if (j == it.nblk[t] - 1) {
               if (lane == 0) umma_commit(&o_full[t]);
               __syncwarp();
@@ -303,7 +307,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
               next_k_ready = true;
               tc_fence_after();
             }
-            issue_s(t, kv_addr0 + slot * AT_TILE_BYTES);
+            issue_s(t, slot);
           }
         }
         if (!ok) break;
