@@ -411,6 +411,16 @@ def secondary_workloads(torch, ops, gi, peaks, dist, world, rank, a, b, c, shard
         out[f"matmul_{S_}"] = {"ms": ms, "TFLOP/s": t, "frac_of_burst_peak": t / tf}
         del aa, bb, cc
 
+    # the pointer-based matmul_kernel on tile-major fp16 buffers (32 x 32 tiles) with leaky_relu, 8192^3:
+    # same kernels, operands fetched through 4-D tensor maps
+    S_ = 8192
+    at = ((torch.rand(S_, S_, device="cuda") - 0.5) / 16).half()
+    bt = ((torch.rand(S_, S_, device="cuda") - 0.5) / 16).half()
+    ms = quick_ms(lambda: ops.matmul(at, bt, "leaky_relu", layout="tile32"), torch, rep=10)
+    t = 2.0 * S_ ** 3 / ms / 1e9
+    out["matmul_tile32_f16_leaky_8192"] = {"ms": ms, "TFLOP/s": t, "frac_of_burst_peak": t / tf}
+    del at, bt
+
     if world > 1:
         # strong scaling of ONE 8192^3 problem: this rank's M-row shard; and the optional all-gather of C
         r0, r1 = sharding.row_shard(M, world, rank)

@@ -98,6 +98,21 @@ int b200k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K,
                      int act, int round_before_bias, void* stream);
 
 /*
+ * C = act(A . B) with A, B and C stored TILE-MAJOR, the memory layout the reference's pointer-based
+ * matmul_kernel addresses (examples/matmul/03-matrix-multiplication.py:333-344 A, :354-362 B,
+ * :378-386 C): the logical [R,S] matrix is cut into 32 x 32 tiles, tile (tr, ts) occupies the 1024
+ * contiguous elements starting at (tr * (S/32) + ts) * 1024, row-major inside the tile
+ * (BLOCK_SIZE_M = BLOCK_SIZE_N = BLOCK_SIZE_K = 32 is the reference's only configuration, :217-222).
+ * M, N, K must be multiples of 32 and the base pointers 16-byte aligned.  f16 = 1: fp16 operands and
+ * output (what the reference kernel stores, :374); f16 = 0: bf16.  act: B200K_ACT_NONE,
+ * B200K_ACT_LEAKY_RELU (the reference's ACTIVATION="leaky_relu", :372-373,391-392) or B200K_ACT_RELU,
+ * applied to the fp32 accumulator before the single round-to-nearest-even downcast.
+ * The tiles go through 4-dimensional TMA tensor maps straight into 64-byte-swizzled operand images in
+ * shared memory (and C tiles back out the same way); there is no separate layout-conversion pass.
+ */
+int b200k_matmul_tile32(const void* A, const void* B, void* C, int M, int N, int K, int act, int f16, void* stream);
+
+/*
  * O = softmax(Q K^T * sm_scale [+ causal mask]) V per (batch, head); q,k,v,o bf16 contiguous
  * [Z,H,N_CTX,D]; lse2[Z,H,N_CTX] fp32 receives m_i + log2(l_i) (base-2 log-sum-exp of the
  * scaled scores), exactly the `M` tensor of the reference.  D must be 64 or 128 and N_CTX a multiple of

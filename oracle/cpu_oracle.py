@@ -52,10 +52,11 @@ def load() -> ctypes.CDLL:
     lib.oracle_golden_matmul.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                                          c_void_p, c_void_p, c_int]
     lib.oracle_golden_matmul_naive.argtypes = [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32]
+    lib.oracle_matmul_kernel_tile32.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int]
     lib.oracle_attn_fwd_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                          c_int, c_float, c_int, c_int]
     for fn in ("oracle_block_range", "oracle_add_f32", "oracle_sin_f32", "oracle_sin_f64_to_f32", "oracle_mul_add_f32",
-               "oracle_golden_matmul", "oracle_golden_matmul_naive", "oracle_attn_fwd_bf16"):
+               "oracle_golden_matmul", "oracle_golden_matmul_naive", "oracle_matmul_kernel_tile32", "oracle_attn_fwd_bf16"):
         getattr(lib, fn).restype = None
     _lib = lib
     return lib
@@ -135,6 +136,34 @@ def golden_matmul(a, b, bias=None, mode: int = 0, activation=""):
     load().oracle_golden_matmul(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, dtype_flag, mode,
                                 bias_full.data_ptr() if bias_full is not None else None,
                                 bias_row.data_ptr() if bias_row is not None else None, _ACT[activation])
+    return out
+
+
+def tilize(t, tile: int = 32):
+    """Row-major [R,S] -> the same shape whose MEMORY holds contiguous tile x tile tiles in row-major tile order
+    (the layout examples/matmul/03-matrix-multiplication.py:333-386 addresses)."""
+    R, S = t.shape
+    assert R % tile == 0 and S % tile == 0
+    return t.reshape(R // tile, tile, S // tile, tile).permute(0, 2, 1, 3).contiguous().view(R, S)
+
+
+def untilize(t, tile: int = 32):
+    """Inverse of tilize."""
+    R, S = t.shape
+    assert R % tile == 0 and S % tile == 0
+    return t.reshape(R // tile, S // tile, tile, tile).permute(0, 2, 1, 3).contiguous().view(R, S)
+
+
+def matmul_kernel_tile32(a_tiled, b_tiled, activation=""):
+    """The reference's pointer-based matmul_kernel on tile-major buffers (tile-major result)."""
+    assert a_tiled.dtype == b_tiled.dtype and a_tiled.dtype in (torch.bfloat16, torch.float16)
+    a, b = _cpu(a_tiled), _cpu(b_tiled)
+    M, K = a.shape
+    K2, N = b.shape
+    assert K == K2 and M % 32 == 0 and N % 32 == 0 and K % 32 == 0
+    out = torch.empty((M, N), dtype=a.dtype)
+    load().oracle_matmul_kernel_tile32(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+                                       0 if a.dtype == torch.bfloat16 else 1, _ACT[activation])
     return out
 
 

@@ -208,6 +208,66 @@ void oracle_golden_matmul_naive(const uint16_t* a, const uint16_t* b, uint16_t* 
   }
 }
 
+/* matmul_kernel, examples/matmul/03-matrix-multiplication.py:241-395, one program (pid_m, pid_n) at a
+ * time with the reference's only configuration BLOCK_SIZE_M = BLOCK_SIZE_N = BLOCK_SIZE_K = 32 (:217-222).
+ * The kernel addresses its operands TILE-MAJOR and ignores the strides it is given:
+ *   A (:333-344)  offset(m, k) = ((m/32) * num_tiles_k + k/32) * 1024 + (m%32) * 32 + k%32, m = offs_m % M (:310)
+ *   B (:354-362)  offset(k, n) = ((k/32) * num_tiles_n + n/32) * 1024 + (k%32) * 32 + n%32, n = offs_n % N (:311)
+ *   C (:378-386)  offset(m, n) = ((m/32) * num_tiles_n + n/32) * 1024 + (m%32) * 32 + n%32
+ * loads are masked with k < K and read 0 otherwise (:347-349,364-366); the accumulator is fp32 over
+ * the k tiles in order (:323-369); optional leaky_relu on the accumulator (:372-373), one downcast
+ * (:374), store masked with m < M and n < N (:388-389).  dtype 1 = fp16 (the reference), 0 = bf16. */
+void oracle_matmul_kernel_tile32(const uint16_t* a, const uint16_t* b, uint16_t* c, int64_t M, int64_t N, int64_t K,
+                                 int dtype, int act) {
+  const int64_t T = 32;
+  const int64_t ntm = (M + T - 1) / T, ntn = (N + T - 1) / T, ntk = (K + T - 1) / T;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t pid_m = 0; pid_m < ntm; ++pid_m) {
+    for (int64_t pid_n = 0; pid_n < ntn; ++pid_n) {
+      float acc[32][32];
+      for (int i = 0; i < 32; ++i)
+        for (int j = 0; j < 32; ++j) acc[i][j] = 0.0f;
+      for (int64_t kt = 0; kt < ntk; ++kt) {
+        float at[32][32], bt[32][32];
+        for (int i = 0; i < 32; ++i) {
+          const int64_t m = (pid_m * T + i) % M;
+          for (int kk = 0; kk < 32; ++kk) {
+            const int64_t k = kt * T + kk;
+            const int64_t off = ((m / T) * ntk + k / T) * (T * T) + (m % T) * T + k % T;
+            at[i][kk] = (k < K) ? h_to_f32(a[off], dtype) : 0.0f;
+          }
+        }
+        for (int kk = 0; kk < 32; ++kk) {
+          const int64_t k = kt * T + kk;
+          for (int j = 0; j < 32; ++j) {
+            const int64_t n = (pid_n * T + j) % N;
+            const int64_t off = ((k / T) * ntn + n / T) * (T * T) + (k % T) * T + n % T;
+            bt[kk][j] = (k < K) ? h_to_f32(b[off], dtype) : 0.0f;
+          }
+        }
+        for (int i = 0; i < 32; ++i)
+          for (int j = 0; j < 32; ++j) {
+            float sum = acc[i][j];
+            for (int kk = 0; kk < 32; ++kk) sum += at[i][kk] * bt[kk][j];
+            acc[i][j] = sum;
+          }
+      }
+      for (int i = 0; i < 32; ++i) {
+        const int64_t om = pid_m * T + i;
+        const int64_t m = om % M;
+        for (int j = 0; j < 32; ++j) {
+          const int64_t on = pid_n * T + j;
+          const int64_t n = on % N;
+          if (om < M && on < N) {
+            const int64_t off = ((m / T) * ntn + n / T) * (T * T) + (m % T) * T + n % T;
+            c[off] = f32_to_h(act_apply(acc[i][j], act), dtype);
+          }
+        }
+      }
+    }
+  }
+}
+
 /* ------------------------------------------------------------------------------------------- */
 /* Fused attention forward                                                                      */
 /* ------------------------------------------------------------------------------------------- */

@@ -16,6 +16,8 @@ ADD_SIZES = [1, 33, 1024, 5000, 98432]
 SIN_SIZES = [32, 1024, 98432]
 MATMUL_SHAPES = [(32, 32, 32), (64, 32, 32), (128, 256, 64), (96, 160, 136), (256, 256, 256)]
 FUSED_SHAPES = [(64, 64, 256), (128, 192, 512)]
+# (M, N, K, ACTIVATION) of the pointer-based matmul_kernel on tile-major fp16 buffers
+TILE32_CASES = [(32, 32, 64, ""), (64, 96, 128, "leaky_relu"), (128, 256, 96, ""), (256, 128, 256, "leaky_relu")]
 # (Z, H, N_CTX, HEAD_DIM, causal, BLOCK_M, BLOCK_N); BLOCK_N <= HEAD_DIM as the reference asserts
 ATTN_CASES = [
     (1, 2, 256, 128, False, 128, 128),
@@ -58,6 +60,26 @@ def fused_inputs(M: int, N: int, K: int, seed: int = 0, dtype=torch.bfloat16):
     return a, b, bias
 
 
+def tile32_inputs(M: int, N: int, K: int, seed: int = 0, dtype=torch.float16):
+    """Row-major A, B ~ U[-0.5, 0.5) in fp16, the distribution of the reference's own check of
+    matmul_kernel (examples/matmul/03-matrix-multiplication.py:431-432)."""
+    g = _gen(seed)
+    a = (torch.rand(M, K, generator=g, dtype=torch.float32) - 0.5).to(dtype)
+    b = (torch.rand(K, N, generator=g, dtype=torch.float32) - 0.5).to(dtype)
+    return a, b
+
+
+def tilize(t: torch.Tensor, tile: int = 32) -> torch.Tensor:
+    """Row-major [R,S] -> same shape, memory holding contiguous tile x tile tiles in row-major tile order."""
+    R, S = t.shape
+    return t.reshape(R // tile, tile, S // tile, tile).permute(0, 2, 1, 3).contiguous().view(R, S)
+
+
+def untilize(t: torch.Tensor, tile: int = 32) -> torch.Tensor:
+    R, S = t.shape
+    return t.reshape(R // tile, S // tile, tile, tile).permute(0, 2, 1, 3).contiguous().view(R, S)
+
+
 def row_bias(N: int, seed: int = 1):
     """bias[N] fp32 ~ N(0, 0.1) of the fused-matmul workload."""
     g = _gen(seed)
@@ -77,7 +99,7 @@ def digest(*tensors) -> str:
     h = hashlib.sha256()
     for t in tensors:
         t = t.contiguous()
-        if t.dtype == torch.bfloat16:
+        if t.dtype in (torch.bfloat16, torch.float16):
             t = t.view(torch.int16)
         h.update(t.numpy().tobytes())
     return h.hexdigest()

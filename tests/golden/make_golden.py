@@ -17,11 +17,12 @@ No reference file is modified or copied into this repository; only the resulting
 stored.
 
 Outputs (small .npz files, a few hundred KB in total):
-  add.npz, sin.npz, matmul.npz, matmul_fused.npz, attention.npz
+  add.npz, sin.npz, matmul.npz, matmul_fused.npz, attention.npz, matmul_tile32.npz
 Inputs are regenerated from their seeds by `golden_inputs.py`; each .npz keeps a sha256 of the
 input bytes so that a drift of torch's CPU RNG cannot silently invalidate the vectors.
 
-Run:  REFERENCE_ROOT=<checkout of the reference> python tests/golden/make_golden.py
+Run:  REFERENCE_ROOT=<checkout of the reference> python tests/golden/make_golden.py [set ...]
+      (sets: add sin matmul matmul_fused attention matmul_tile32; default all)
 """
 from __future__ import annotations
 
@@ -52,6 +53,7 @@ KERNEL_SOURCES = {
     "ref_matmul": ("examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py", ["matmul_kernel_tma"]),
     "ref_fused": ("python/tutorials/09-matmul-fused.py", ["matmul_kernel_fused"]),
     "ref_attn": ("examples/fused-attn/06-fused-attention.py", ["_attn_fwd_inner", "_maybe_make_tensor_desc", "_attn_fwd"]),
+    "ref_mm03": ("examples/matmul/03-matrix-multiplication.py", ["leaky_relu", "matmul_kernel"]),
 }
 
 HEADER = "import triton\nimport triton.language as tl\n\n"
@@ -120,84 +122,111 @@ def _bits(t: torch.Tensor) -> np.ndarray:
 def main():
     from triton.tools.tensor_descriptor import TensorDescriptor
     _patch_interpreter_dot()
+    only = set(sys.argv[1:])
+
+    def want(name):
+        return not only or name in only
+
     with tempfile.TemporaryDirectory() as td:
         k = _load_kernels(Path(td))
 
-        # ---- add_kernel (python/tutorials/01-vector-add.py:29-54), launch as in add() :75
-        out = {}
-        for n in gi.ADD_SIZES:
-            x, y = gi.add_inputs(n)
-            o = torch.empty_like(x)
-            k["ref_add"].add_kernel[((n + 1023) // 1024,)](x, y, o, n, BLOCK_SIZE=1024)
-            out[f"in_sha_{n}"], out[f"out_{n}"] = np.array(gi.digest(x, y)), o.numpy()
-        np.savez_compressed(HERE / "add.npz", **out)
+        if want("add"):
+            # ---- add_kernel (python/tutorials/01-vector-add.py:29-54), launch as in add() :75
+            out = {}
+            for n in gi.ADD_SIZES:
+                x, y = gi.add_inputs(n)
+                o = torch.empty_like(x)
+                k["ref_add"].add_kernel[((n + 1023) // 1024,)](x, y, o, n, BLOCK_SIZE=1024)
+                out[f"in_sha_{n}"], out[f"out_{n}"] = np.array(gi.digest(x, y)), o.numpy()
+            np.savez_compressed(HERE / "add.npz", **out)
 
-        # ---- sin_kernel (examples/01-sin-kernel.py:17-29)
-        out = {}
-        for n in gi.SIN_SIZES:
-            x = gi.sin_inputs(n)
-            o = torch.empty_like(x)
-            k["ref_sin"].sin_kernel[((n + 1023) // 1024,)](x, o, n, BLOCK_SIZE=1024)
-            out[f"in_sha_{n}"], out[f"out_{n}"] = np.array(gi.digest(x)), o.numpy()
-        np.savez_compressed(HERE / "sin.npz", **out)
+        if want("sin"):
+            # ---- sin_kernel (examples/01-sin-kernel.py:17-29)
+            out = {}
+            for n in gi.SIN_SIZES:
+                x = gi.sin_inputs(n)
+                o = torch.empty_like(x)
+                k["ref_sin"].sin_kernel[((n + 1023) // 1024,)](x, o, n, BLOCK_SIZE=1024)
+                out[f"in_sha_{n}"], out[f"out_{n}"] = np.array(gi.digest(x)), o.numpy()
+            np.savez_compressed(HERE / "sin.npz", **out)
 
-        # ---- matmul_kernel_tma (09-persistent-matmul.ttnn.py:105-143), the reference's 32x32x32 config :77-86
-        out = {}
-        for (M, N, K) in gi.MATMUL_SHAPES:
-            a, b = gi.matmul_inputs(M, N, K)
-            c = torch.full((M, N), 7.5, dtype=torch.bfloat16)
-            BM = BN = BK = 32
-            ad = TensorDescriptor.from_tensor(a, [BM, BK])
-            bd = TensorDescriptor.from_tensor(b, [BK, BN])
-            cd = TensorDescriptor.from_tensor(c, [BM, BN])
-            grid = (((M + BM - 1) // BM) * ((N + BN - 1) // BN),)
-            k["ref_matmul"].matmul_kernel_tma[grid](ad, bd, cd, M, N, K, BLOCK_SIZE_M=BM, BLOCK_SIZE_N=BN,
-                                                    BLOCK_SIZE_K=BK, GROUP_SIZE_M=1, FP8_OUTPUT=False,
-                                                    WARP_SPECIALIZE=False)
-            tag = f"{M}x{N}x{K}"
-            out[f"in_sha_{tag}"], out[f"c_{tag}"] = np.array(gi.digest(a, b)), _bits(c)
-        np.savez_compressed(HERE / "matmul.npz", **out)
+        if want("matmul"):
+            # ---- matmul_kernel_tma (09-persistent-matmul.ttnn.py:105-143), the reference's 32x32x32 config :77-86
+            out = {}
+            for (M, N, K) in gi.MATMUL_SHAPES:
+                a, b = gi.matmul_inputs(M, N, K)
+                c = torch.full((M, N), 7.5, dtype=torch.bfloat16)
+                BM = BN = BK = 32
+                ad = TensorDescriptor.from_tensor(a, [BM, BK])
+                bd = TensorDescriptor.from_tensor(b, [BK, BN])
+                cd = TensorDescriptor.from_tensor(c, [BM, BN])
+                grid = (((M + BM - 1) // BM) * ((N + BN - 1) // BN),)
+                k["ref_matmul"].matmul_kernel_tma[grid](ad, bd, cd, M, N, K, BLOCK_SIZE_M=BM, BLOCK_SIZE_N=BN,
+                                                        BLOCK_SIZE_K=BK, GROUP_SIZE_M=1, FP8_OUTPUT=False,
+                                                        WARP_SPECIALIZE=False)
+                tag = f"{M}x{N}x{K}"
+                out[f"in_sha_{tag}"], out[f"c_{tag}"] = np.array(gi.digest(a, b)), _bits(c)
+            np.savez_compressed(HERE / "matmul.npz", **out)
 
-        # ---- matmul_kernel_fused (python/tutorials/09-matmul-fused.py:105-148): bias [M,N] added after the
-        #      downcast.  The reference hard-codes float16 as the output type (:115), so these vectors are
-        #      generated with fp16 operands exactly as that file runs; they pin the oracle's fp16 mode.
-        out = {}
-        for (M, N, K) in gi.FUSED_SHAPES:
-            a, b, bias = gi.fused_inputs(M, N, K, dtype=torch.float16)
-            c = torch.empty((M, N), dtype=torch.float16)
-            BM, BN, BK = 64, 64, 256  # the reference's config :74-83
-            ad = TensorDescriptor.from_tensor(a, [BM, BK])
-            bd = TensorDescriptor.from_tensor(b, [BK, BN])
-            cd = TensorDescriptor.from_tensor(c, [BM, BN])
-            biasd = TensorDescriptor.from_tensor(bias, [BM, BN])
-            grid = (((M + BM - 1) // BM) * ((N + BN - 1) // BN),)
-            k["ref_fused"].matmul_kernel_fused[grid](ad, bd, cd, biasd, M, N, K, BLOCK_SIZE_M=BM, BLOCK_SIZE_N=BN,
-                                                     BLOCK_SIZE_K=BK, GROUP_SIZE_M=1, FP8_OUTPUT=False,
-                                                     WARP_SPECIALIZE=False)
-            tag = f"{M}x{N}x{K}"
-            out[f"in_sha_{tag}"], out[f"c_{tag}"] = np.array(gi.digest(a, b, bias)), c.numpy()
-        np.savez_compressed(HERE / "matmul_fused.npz", **out)
+        if want("matmul_fused"):
+            # ---- matmul_kernel_fused (python/tutorials/09-matmul-fused.py:105-148): bias [M,N] added after the
+            #      downcast.  The reference hard-codes float16 as the output type (:115), so these vectors are
+            #      generated with fp16 operands exactly as that file runs; they pin the oracle's fp16 mode.
+            out = {}
+            for (M, N, K) in gi.FUSED_SHAPES:
+                a, b, bias = gi.fused_inputs(M, N, K, dtype=torch.float16)
+                c = torch.empty((M, N), dtype=torch.float16)
+                BM, BN, BK = 64, 64, 256  # the reference's config :74-83
+                ad = TensorDescriptor.from_tensor(a, [BM, BK])
+                bd = TensorDescriptor.from_tensor(b, [BK, BN])
+                cd = TensorDescriptor.from_tensor(c, [BM, BN])
+                biasd = TensorDescriptor.from_tensor(bias, [BM, BN])
+                grid = (((M + BM - 1) // BM) * ((N + BN - 1) // BN),)
+                k["ref_fused"].matmul_kernel_fused[grid](ad, bd, cd, biasd, M, N, K, BLOCK_SIZE_M=BM, BLOCK_SIZE_N=BN,
+                                                         BLOCK_SIZE_K=BK, GROUP_SIZE_M=1, FP8_OUTPUT=False,
+                                                         WARP_SPECIALIZE=False)
+                tag = f"{M}x{N}x{K}"
+                out[f"in_sha_{tag}"], out[f"c_{tag}"] = np.array(gi.digest(a, b, bias)), c.numpy()
+            np.savez_compressed(HERE / "matmul_fused.npz", **out)
 
-        # ---- _attn_fwd (examples/fused-attn/06-fused-attention.py:143-215), launched as _attention.forward :257-267
-        out = {}
-        for (Z, H, S, D, causal, BM, BN) in gi.ATTN_CASES:
-            q, kk, v = gi.attn_inputs(Z, H, S, D)
-            sm_scale = D ** -0.5
-            o = torch.empty_like(q)
-            M = torch.empty((Z, H, S), dtype=torch.float32)
-            y = Z * H * S
-            dq = TensorDescriptor(q, shape=[y, D], strides=[D, 1], block_shape=[BM, D])
-            dk = TensorDescriptor(kk, shape=[y, D], strides=[D, 1], block_shape=[BN, D])
-            dv = TensorDescriptor(v, shape=[y, D], strides=[D, 1], block_shape=[BN, D])
-            do = TensorDescriptor(o, shape=[y, D], strides=[D, 1], block_shape=[BM, D])
-            grid = ((S + BM - 1) // BM, Z * H, 1)
-            k["ref_attn"]._attn_fwd[grid](sm_scale, M, Z, H, dq, dk, dv, do, N_CTX=S, HEAD_DIM=D, BLOCK_M=BM,
-                                          BLOCK_N=BN, FP8_OUTPUT=False, STAGE=3 if causal else 1,
-                                          warp_specialize=False, IS_HOPPER=False)
-            tag = f"{Z}x{H}x{S}x{D}_{'c' if causal else 'n'}_{BM}x{BN}"
-            out[f"in_sha_{tag}"] = np.array(gi.digest(q, kk, v))
-            out[f"o_{tag}"], out[f"M_{tag}"] = _bits(o), M.numpy()
-        np.savez_compressed(HERE / "attention.npz", **out)
+        if want("attention"):
+            # ---- _attn_fwd (examples/fused-attn/06-fused-attention.py:143-215), launched as _attention.forward :257-267
+            out = {}
+            for (Z, H, S, D, causal, BM, BN) in gi.ATTN_CASES:
+                q, kk, v = gi.attn_inputs(Z, H, S, D)
+                sm_scale = D ** -0.5
+                o = torch.empty_like(q)
+                M = torch.empty((Z, H, S), dtype=torch.float32)
+                y = Z * H * S
+                dq = TensorDescriptor(q, shape=[y, D], strides=[D, 1], block_shape=[BM, D])
+                dk = TensorDescriptor(kk, shape=[y, D], strides=[D, 1], block_shape=[BN, D])
+                dv = TensorDescriptor(v, shape=[y, D], strides=[D, 1], block_shape=[BN, D])
+                do = TensorDescriptor(o, shape=[y, D], strides=[D, 1], block_shape=[BM, D])
+                grid = ((S + BM - 1) // BM, Z * H, 1)
+                k["ref_attn"]._attn_fwd[grid](sm_scale, M, Z, H, dq, dk, dv, do, N_CTX=S, HEAD_DIM=D, BLOCK_M=BM,
+                                              BLOCK_N=BN, FP8_OUTPUT=False, STAGE=3 if causal else 1,
+                                              warp_specialize=False, IS_HOPPER=False)
+                tag = f"{Z}x{H}x{S}x{D}_{'c' if causal else 'n'}_{BM}x{BN}"
+                out[f"in_sha_{tag}"] = np.array(gi.digest(q, kk, v))
+                out[f"o_{tag}"], out[f"M_{tag}"] = _bits(o), M.numpy()
+            np.savez_compressed(HERE / "attention.npz", **out)
+        if want("matmul_tile32"):
+            # ---- matmul_kernel (examples/matmul/03-matrix-multiplication.py:241-395) on TILE-MAJOR buffers, launched
+            #      as matmul() does (:413-420) with the reference's only configuration 32x32x32, GROUP_SIZE_M=1
+            #      (:217-222).  The kernel ignores the strides; the stored result is the raw (tile-major) C buffer.
+            out = {}
+            for (M, N, K, activation) in gi.TILE32_CASES:
+                a, b = gi.tile32_inputs(M, N, K)
+                at, bt = gi.tilize(a), gi.tilize(b)
+                c = torch.full((M, N), 7.5, dtype=torch.float16)
+                grid = ((M // 32) * (N // 32),)
+                k["ref_mm03"].matmul_kernel[grid](at, bt, c, M, N, K, at.stride(0), at.stride(1), bt.stride(0),
+                                                  bt.stride(1), c.stride(0), c.stride(1), BLOCK_SIZE_M=32,
+                                                  BLOCK_SIZE_N=32, BLOCK_SIZE_K=32, GROUP_SIZE_M=1,
+                                                  ACTIVATION=activation)
+                tag = f"{M}x{N}x{K}_{activation or 'none'}"
+                out[f"in_sha_{tag}"], out[f"c_{tag}"] = np.array(gi.digest(a, b)), c.numpy()
+            np.savez_compressed(HERE / "matmul_tile32.npz", **out)
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")
 

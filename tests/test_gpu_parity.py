@@ -268,6 +268,55 @@ def test_matmul_fp16_example_shapes_and_activation():
             assert float((got.view(torch.int16) != ref.view(torch.int16)).float().mean()) < 1e-2
 
 
+@pytest.mark.parametrize("case", gi.TILE32_CASES)
+def test_matmul_tile32_golden(golden_dir, case):
+    # tile-major buffers in, tile-major buffer out, against what the reference's matmul_kernel source wrote
+    M, N, K, act = case
+    g = np.load(golden_dir / "matmul_tile32.npz")
+    a, b = gi.tile32_inputs(M, N, K)
+    golden = torch.from_numpy(g[f"c_{M}x{N}x{K}_{act or 'none'}"])
+    got = ops.matmul(gi.tilize(a).cuda(), gi.tilize(b).cuda(), activation=act, layout="tile32").cpu()
+    assert got.dtype == torch.float16
+    assert oracle.rel_frobenius(got.float(), golden.float()) <= MATMUL_REL_FRO
+    diff = (got.float() - golden.float()).abs()
+    assert float(diff.max()) <= float(golden.float().abs().max()) * 2 ** -9
+    assert float((diff > 0).float().mean()) < 1e-2
+
+
+@pytest.mark.parametrize("shape,dtype", [((32, 32, 32), torch.float16), ((160, 96, 224), torch.float16),
+                                          ((384, 640, 416), torch.bfloat16), ((2304, 2304, 160), torch.float16),
+                                          ((2560, 4608, 96), torch.bfloat16)])
+def test_matmul_tile32_oracle_shapes(shape, dtype):
+    # single-CTA kernels (few tiles) and the CTA-pair kernel (>= 74 tiles of 256 x 256), with tile rows / columns that
+    # end inside a 128 / 256-wide kernel tile; sentinel-filled C catches unwritten tiles
+    M, N, K = shape
+    a, b = gi.matmul_inputs(M, N, K, seed=21, dtype=dtype)
+    for act in ("", "leaky_relu"):
+        c = torch.full((M, N), 7.5, dtype=dtype, device="cuda")
+        kernels.matmul_kernel[lambda META: (-(-M // META["BLOCK_SIZE_M"]) * -(-N // META["BLOCK_SIZE_N"]),)](
+            gi.tilize(a).cuda(), gi.tilize(b).cuda(), c, M, N, K, K, 1, N, 1, N, 1, ACTIVATION=act, LAYOUT="tile32")
+        ref = oracle.matmul_kernel_tile32(gi.tilize(a), gi.tilize(b), act)
+        got = c.cpu()
+        assert oracle.rel_frobenius(got.float(), ref.float()) <= MATMUL_REL_FRO
+        assert float((got.view(torch.int16) != ref.view(torch.int16)).float().mean()) < 2e-2
+        # and the logical result equals the row-major path's, bit for bit (same kernel, same shared-memory image)
+        row = ops.matmul(a.cuda(), b.cuda(), activation=act).cpu()
+        assert torch.equal(ops.untilize(got).view(torch.int16), row.view(torch.int16))
+
+
+def test_matmul_tile32_rejects_bad_arguments():
+    t = torch.zeros(64, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        ops.matmul(torch.zeros(48, 64, dtype=torch.float16, device="cuda"), t, layout="tile32")
+    with pytest.raises(ValueError):
+        ops.matmul(t, t, layout="tile16")
+    lib = _lib.load()
+    rc = lib.b200k_matmul_tile32(t.data_ptr(), t.data_ptr(), t.data_ptr(), 64, 40, 64, 0, 1, None)
+    assert rc == _lib.ERR_INVALID_ARG and "multiples of 32" in _lib.last_error()
+    rc = lib.b200k_matmul_tile32(t.data_ptr(), t.data_ptr(), t.data_ptr(), 64, 64, 64, 0, 2, None)
+    assert rc == _lib.ERR_INVALID_ARG
+
+
 def test_matmul_rejects_bad_arguments():
     a = torch.zeros(64, 36, dtype=torch.bfloat16, device="cuda")      # 72-byte rows
     b = torch.zeros(36, 64, dtype=torch.bfloat16, device="cuda")

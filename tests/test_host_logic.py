@@ -35,7 +35,8 @@ def recording(monkeypatch):
     RecordingLauncher.calls = []
     monkeypatch.setattr(driver.active, "launcher_cls", RecordingLauncher)
     monkeypatch.setattr(driver.active, "get_current_stream", lambda device_id=None: 0)
-    for k in (kernels.add_kernel, kernels.sin_kernel, kernels.matmul_kernel_tma, kernels.matmul_kernel_fused, kernels._attn_fwd):
+    for k in (kernels.add_kernel, kernels.sin_kernel, kernels.matmul_kernel_tma, kernels.matmul_kernel_fused,
+              kernels.matmul_kernel, kernels._attn_fwd):
         monkeypatch.setattr(k, "launcher", None)
     return RecordingLauncher.calls
 
@@ -69,6 +70,43 @@ def test_descriptor_flattening_matches_reference_order(recording):
     first = [v for _, v in flat[:10]]
     assert first == [a.data_ptr(), M, K, K, 1, 0, M, K, K, 1]
     assert [v for _, v in flat[-3:]] == [M, N, K]
+
+
+def test_pointer_matmul_kernel_launch_surface(recording):
+    # matmul_kernel[grid](a, b, c, M, N, K, 6 strides, ACTIVATION=...), examples/matmul/03-matrix-multiplication.py:413-420
+    M, N, K = 256, 512, 128
+    a, b, c = (fake(torch.zeros(s, dtype=torch.float16)) for s in ((M, K), (K, N), (M, N)))
+    grid = lambda META: (-(-M // META["BLOCK_SIZE_M"]) * -(-N // META["BLOCK_SIZE_N"]),)
+    kernels.matmul_kernel[grid](a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0),
+                                c.stride(1), ACTIVATION="leaky_relu")
+    call = recording[0]
+    assert call["function"] == "matmul_kernel:BLOCK_SIZE_M=128,BLOCK_SIZE_N=256,ACTIVATION=2,F16=1,TILE32=0"
+    assert [k for k, _ in call["flat"]] == [_lib.ARG_PTR] * 3 + [_lib.ARG_I32] * 9   # constexprs are dropped
+    assert [v for _, v in call["flat"][3:]] == [M, N, K, K, 1, N, 1, N, 1]
+    kernels.matmul_kernel[grid](a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0),
+                                c.stride(1), ACTIVATION="", LAYOUT="tile32")
+    assert recording[1]["function"].endswith("ACTIVATION=0,F16=1,TILE32=1")
+    with pytest.raises(ValueError):
+        kernels.matmul_kernel[grid](a, b, c, M, N, K, K, 1, N, 1, N, 1, ACTIVATION="gelu")
+    with pytest.raises(ValueError):
+        kernels.matmul_kernel[grid](a, b, c, M, N, K, K, 1, N, 1, N, 1, LAYOUT="tile64")
+
+
+def test_tilize_round_trip_and_addressing():
+    # element (r, c) of the logical matrix sits at ((r/32)*(S/32) + c/32)*1024 + (r%32)*32 + c%32
+    # (examples/matmul/03-matrix-multiplication.py:333-344)
+    from triton_tenstorrent_b200 import ops
+    R, S = 96, 160
+    t = torch.arange(R * S, dtype=torch.float32).reshape(R, S)
+    tiled = ops.tilize(t)
+    flat = tiled.reshape(-1)
+    for (r, c) in ((0, 0), (31, 31), (32, 0), (5, 47), (95, 159), (64, 33)):
+        off = ((r // 32) * (S // 32) + c // 32) * 1024 + (r % 32) * 32 + c % 32
+        assert flat[off] == t[r, c]
+    assert torch.equal(ops.untilize(tiled), t)
+    assert torch.equal(tiled, oracle.tilize(t))
+    with pytest.raises(ValueError):
+        ops.tilize(torch.zeros(40, 64))
 
 
 def test_attention_launch_surface(recording):

@@ -81,6 +81,25 @@ def test_matmul_fused_golden_fp16(golden_dir, shape):
     assert oracle.rel_frobenius(single.float(), golden.float()) < 1e-3
 
 
+@pytest.mark.parametrize("case", gi.TILE32_CASES)
+def test_matmul_kernel_tile32_golden(golden_dir, case):
+    # the pointer-based matmul_kernel on tile-major buffers (examples/matmul/03-matrix-multiplication.py:241-395)
+    M, N, K, act = case
+    g = np.load(golden_dir / "matmul_tile32.npz")
+    a, b = gi.tile32_inputs(M, N, K)
+    tag = f"{M}x{N}x{K}_{act or 'none'}"
+    assert str(g[f"in_sha_{tag}"]) == gi.digest(a, b)
+    golden = torch.from_numpy(g[f"c_{tag}"])            # the raw, tile-major C buffer the kernel wrote
+    out = oracle.matmul_kernel_tile32(gi.tilize(a), gi.tilize(b), act)
+    diff = (out.float() - golden.float()).abs()
+    assert float(diff.max()) <= float(golden.float().abs().max()) * 2 ** -10   # one fp16 ulp (summation order)
+    assert float((diff > 0).float().mean()) < 5e-3
+    # the tile-major kernel computes the same logical product as the row-major one, bit for bit in the oracle
+    row = oracle.golden_matmul(a, b, activation=act)
+    assert torch.equal(oracle.untilize(out).view(torch.int16), row.view(torch.int16))
+    assert torch.equal(oracle.tilize(oracle.untilize(out)).view(torch.int16), out.view(torch.int16))
+
+
 @pytest.mark.parametrize("case", gi.ATTN_CASES)
 def test_attention_golden(golden_dir, case):
     Z, H, S, D, causal, BM, BN = case

@@ -99,16 +99,17 @@ struct TmapKey {
   uintptr_t base;
   uint64_t inner, outer, ld;
   uint32_t box_inner, box_outer;
+  uint32_t kind;  // 0 = row-major 2-D, 1 = tile-major 4-D
   bool operator==(const TmapKey& o) const {
     return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld && box_inner == o.box_inner &&
-           box_outer == o.box_outer;
+           box_outer == o.box_outer && kind == o.kind;
   }
 };
 struct TmapKeyHash {
   size_t operator()(const TmapKey& k) const {
     uint64_t h = 1469598103934665603ull;
     auto mix = [&h](uint64_t v) { h = (h ^ v) * 1099511628211ull; };
-    mix(k.base); mix(k.inner); mix(k.outer); mix(k.ld); mix(k.box_inner); mix(k.box_outer);
+    mix(k.base); mix(k.inner); mix(k.outer); mix(k.ld); mix(k.box_inner); mix(k.box_outer); mix(k.kind);
     return static_cast<size_t>(h);
   }
 };
@@ -117,7 +118,7 @@ static std::mutex g_tmap_mutex;
 
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer) {
-  TmapKey key{reinterpret_cast<uintptr_t>(base), inner, outer, ld, box_inner, box_outer};
+  TmapKey key{reinterpret_cast<uintptr_t>(base), inner, outer, ld, box_inner, box_outer, 0};
   {
     std::lock_guard<std::mutex> lock(g_tmap_mutex);
     auto it = g_tmaps.find(key);
@@ -143,6 +144,45 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
     return set_error(B200K_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, pitch %llu, box %u x %u)",
                      static_cast<int>(r), (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)ld,
                      box_inner, box_outer);
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    if (g_tmaps.size() > 4096) g_tmaps.clear();
+    g_tmaps.emplace(key, *out);
+  }
+  return B200K_OK;
+}
+
+int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows) {
+  const uint32_t box_cols = 32;
+  TmapKey key{reinterpret_cast<uintptr_t>(base), cols, rows, 0, box_cols, box_rows, 1};
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    auto it = g_tmaps.find(key);
+    if (it != g_tmaps.end()) {
+      *out = it->second;
+      return B200K_OK;
+    }
+  }
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) return set_error(B200K_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    return set_error(B200K_ERR_INVALID_ARG, "tensor map: base must be 16-byte aligned");
+  if (cols == 0 || rows == 0 || (cols & 31) || (rows & 31))
+    return set_error(B200K_ERR_INVALID_ARG, "tile-major tensor map: %llu x %llu is not a whole number of 32 x 32 tiles",
+                     (unsigned long long)rows, (unsigned long long)cols);
+  if (box_rows == 0 || (box_rows & 31) || box_rows > 256)
+    return set_error(B200K_ERR_INVALID_ARG, "tile-major tensor map: box %u x %u not supported", box_rows, box_cols);
+  const uint64_t tile_bytes = 32 * 32 * 2;
+  cuuint64_t dims[4] = {32, cols / 32, 32, rows / 32};
+  cuuint64_t strides[3] = {tile_bytes, 32 * 2, (cols / 32) * tile_bytes};  // next tile column, next row in tile, next tile row
+  cuuint32_t box[4] = {32, 1, 32, box_rows / 32};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(B200K_ERR_CUDA, "cuTensorMapEncodeTiled (tile-major) failed with CUresult %d (%llu x %llu, box %u x %u)",
+                     static_cast<int>(r), (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);
   {
     std::lock_guard<std::mutex> lock(g_tmap_mutex);
     if (g_tmaps.size() > 4096) g_tmaps.clear();
@@ -269,6 +309,36 @@ static int generic_launch(const char* kernel_name, int gx, int gy, int gz, cudaS
     ma.dtype = spec_value(spec, "F16", 0) ? 1 : 0;  // descriptors do not carry the element type
     return matmul_bf16(ma, stream, nullptr);
   }
+  if (name == "matmul_kernel") {
+    // a_ptr, b_ptr, c_ptr, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn
+    // (examples/matmul/03-matrix-multiplication.py:413-420).  TILE32=1: the buffers are tile-major, as the
+    // reference kernel addresses them (it ignores the strides); otherwise row-major with the given strides.
+    void* pa = c.ptr(); void* pb = c.ptr(); void* pc = c.ptr();
+    const int64_t M = c.integer(), N = c.integer(), K = c.integer();
+    int64_t st[6];
+    for (int i = 0; i < 6; ++i) st[i] = c.integer();
+    if (c.fail || c.i != nargs)
+      return set_error(B200K_ERR_INVALID_ARG, "launch matmul_kernel: expected 3 pointers, M, N, K and 6 strides, got %d arguments", nargs);
+    if (gy != 1 || gz != 1) return set_error(B200K_ERR_INVALID_ARG, "launch matmul_kernel: 1-D grid expected");
+    const long bm = spec_value(spec, "BLOCK_SIZE_M", 0), bn = spec_value(spec, "BLOCK_SIZE_N", 0);
+    if (bm > 0 && bn > 0) {
+      const int64_t need = ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
+      if (gx < need) return set_error(B200K_ERR_INVALID_ARG, "launch matmul_kernel: grid %d smaller than the %lld output tiles", gx, (long long)need);
+    }
+    const long act = spec_value(spec, "ACTIVATION", B200K_ACT_NONE);
+    MatmulArgs ma{};
+    ma.A = pa; ma.B = pb; ma.C = pc;
+    ma.M = (int)M; ma.N = (int)N; ma.K = (int)K;
+    ma.act = (int)act;
+    ma.dtype = spec_value(spec, "F16", 1) ? 1 : 0;  // the reference kernel stores fp16
+    ma.tile32 = spec_value(spec, "TILE32", 0) ? 1 : 0;
+    if (!ma.tile32) {
+      if (st[1] != 1 || st[3] != 1 || st[5] != 1)
+        return set_error(B200K_ERR_INVALID_ARG, "launch matmul_kernel: row-major operands must have unit inner stride");
+      ma.lda = st[0]; ma.ldb = st[2]; ma.ldc = st[4];
+    }
+    return matmul_bf16(ma, stream, nullptr);
+  }
   if (name == "_attn_fwd") {
     const float sm_scale = c.f32();
     float* lse = static_cast<float*>(c.ptr());
@@ -342,6 +412,13 @@ int b200k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K,
                      const void* bias, int bias_kind, int64_t ldbias, int act, int round_before_bias, void* stream) {
   clear_error();
   MatmulArgs a{A, B, C, M, N, K, lda, ldb, ldc, bias, bias_kind, ldbias, act, round_before_bias, 1};
+  return matmul_bf16(a, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int b200k_matmul_tile32(const void* A, const void* B, void* C, int M, int N, int K, int act, int f16, void* stream) {
+  clear_error();
+  if (f16 != 0 && f16 != 1) return set_error(B200K_ERR_INVALID_ARG, "matmul_tile32: f16 must be 0 or 1 (got %d)", f16);
+  MatmulArgs a{A, B, C, M, N, K, 0, 0, 0, nullptr, B200K_BIAS_NONE, 0, act, 0, f16, 1};
   return matmul_bf16(a, static_cast<cudaStream_t>(stream), nullptr);
 }
 

@@ -42,6 +42,11 @@ void count_launch();
 // out-of-bounds reads fill with zero.  Cached per (base, dims, pitch, box).
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer);
+// 4-D tensor map of a `rows` x `cols` matrix stored tile-major (contiguous 32 x 32 tiles, tiles in
+// row-major order; rows and cols multiples of 32): dimensions (column in tile, tile column, row in
+// tile, tile row), box = box_rows x 32 elements (one tile column, box_rows a multiple of 32),
+// 64-byte swizzle, so the box lands as box_rows dense rows of 64 bytes.
+int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows);
 
 // Kernel launchers (one translation unit each).
 int add_f32(const float* x, const float* y, float* out, int64_t n, cudaStream_t s);
@@ -60,6 +65,7 @@ struct MatmulArgs {
   int act;
   int round_before_bias;
   int dtype;  // 0 = bf16, 1 = fp16 (A, B, C and a full [M,N] bias)
+  int tile32; // 1 = A, B and C are stored tile-major (32 x 32 tiles); lda/ldb/ldc are ignored, no bias
 };
 // status_override: device word the kernel reports bounded-wait failures to (nullptr = the
 // per-device word from current_device_info()).

@@ -41,10 +41,16 @@ struct MatmulParams {
   int64_t ldbias;
   int act;
   int round_before_bias;
-  uint32_t b_lbo, b_sbo, b_kstep;  // MN-major B descriptor strides (bytes)
+  // Operand images in shared memory (bytes).  Row-major operands: 128-byte swizzle, A rows of 64 k
+  // (k step +32 B), B boxes of 64 k-rows x 64 n.  Tile-major operands: 64-byte swizzle, A as two
+  // 128 x 32 halves, B boxes of 64 k-rows x 32 n.
+  uint32_t swz;                    // UMMA layout type of both operands
+  uint32_t a_sbo, a_khalf;         // A: 8-row group pitch; offset of k-steps 2,3 (k >= 32) from k-steps 0,1
+  uint32_t b_lbo, b_sbo, b_kstep;  // MN-major B: pitch of N chunks, of 8 k-row groups, of one k step (16 rows)
   int f16;                         // operands, bias[M,N] and C are fp16 instead of bf16
   uint32_t idesc;                  // UMMA instruction descriptor (tile shape, operand formats and majors)
   int l2_hint;                     // CTA-pair kernel: 0 = no hints, 1 = A evict_last / B evict_first, 2 = A evict_last only
+  int tile32;                      // A, B, C stored as contiguous 32 x 32 tiles (4-D tensor maps, tile coordinates)
   uint32_t* status;
 };
 
@@ -164,17 +170,33 @@ __device__ __forceinline__ void epilogue_chunk(const MatmulParams& p, const CUte
     // ---- staging buffer `buf` must no longer be read by the TMA store issued two chunks ago
     if (lane == 0) tma_store_wait_read<1>();
     __syncwarp();
-    uint8_t* dst = my_stage + buf * MM_C_BUF_BYTES + lane * 128;
+    uint8_t* stage_buf = my_stage + buf * MM_C_BUF_BYTES;
+    if (p.tile32) {
+      // two 32 x 32 tiles side by side, each 32 rows of 64 bytes with the 64-byte swizzle
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-      *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = val;
+      for (int j = 0; j < 8; ++j) {
+        const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        *reinterpret_cast<uint4*>(stage_buf + (j >> 2) * 2048 + lane * 64 + (((j & 3) ^ ((lane >> 1) & 3)) << 4)) = val;
+      }
+    } else {
+      uint8_t* dst = stage_buf + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = val;
+      }
     }
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      if (row0_warp < p.M && col0 < p.N)
-        tma_store_2d(tmap_c, my_stage + buf * MM_C_BUF_BYTES, col0, row0_warp);
+      if (row0_warp < p.M && col0 < p.N) {
+        if (p.tile32) {
+          tma_store_tile32(tmap_c, stage_buf, col0 >> 5, row0_warp >> 5);
+          if (col0 + 32 < p.N) tma_store_tile32(tmap_c, stage_buf + 2048, (col0 >> 5) + 1, row0_warp >> 5);
+        } else {
+          tma_store_2d(tmap_c, stage_buf, col0, row0_warp);
+        }
+      }
       tma_store_commit();
     }
     buf ^= 1;
@@ -241,11 +263,23 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&full_bar[stage], MM_A_STAGE_BYTES + L::B_STAGE_BYTES);
-          tma_load_2d(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, &full_bar[stage], kb * MM_BK, m0);
+          if (p.tile32) {
+            // tile-major operands: A as two 128 x 32 halves, B as BN/32 boxes of 64 k-rows x 32 n; tile coordinates
 #pragma unroll
-          for (int i = 0; i < BN / 64; ++i)
-            tma_load_2d(smem_b + stage * L::B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, &full_bar[stage],
-                        n0 + i * 64, kb * MM_BK);
+            for (int j = 0; j < 2; ++j)
+              tma_load_tile32(smem_a + stage * MM_A_STAGE_BYTES + j * (MM_A_STAGE_BYTES / 2), &tmap_a, &full_bar[stage],
+                              kb * 2 + j, m0 >> 5);
+#pragma unroll
+            for (int i = 0; i < BN / 32; ++i)
+              tma_load_tile32(smem_b + stage * L::B_STAGE_BYTES + i * (MM_B_BOX_BYTES / 2), &tmap_b, &full_bar[stage],
+                              (n0 >> 5) + i, kb * 2);
+          } else {
+            tma_load_2d(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, &full_bar[stage], kb * MM_BK, m0);
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(smem_b + stage * L::B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, &full_bar[stage],
+                          n0 + i * 64, kb * MM_BK);
+          }
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -273,8 +307,9 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
           const uint32_t b_addr = smem_u32(smem_b + stage * L::B_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < MM_BK / MM_UMMA_K; ++k) {
-            const uint64_t a_desc = umma_smem_desc_sw128(a_addr + k * (MM_UMMA_K * 2), 16, 1024);
-            const uint64_t b_desc = umma_smem_desc_sw128(b_addr + k * p.b_kstep, p.b_lbo, p.b_sbo);
+            const uint64_t a_desc = umma_smem_desc(a_addr + (k >> 1) * p.a_khalf + (k & 1) * (MM_UMMA_K * 2), 16,
+                                                   p.a_sbo, p.swz);
+            const uint64_t b_desc = umma_smem_desc(b_addr + k * p.b_kstep, p.b_lbo, p.b_sbo, p.swz);
             umma_ss(d_tmem, a_desc, b_desc, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // slot reusable once these MMAs have read it
@@ -425,11 +460,22 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
         if (lane == 0) {
           const uint32_t leader_full = mapa_shared(smem_u32(&full_bar[stage]), 0);
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * MM2_STAGE_BYTES);
-          tma_load_2d_2cta_hint(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, leader_full, kb * MM_BK, m0, pol_a);
+          if (p.tile32) {
 #pragma unroll
-          for (int i = 0; i < 2; ++i)
-            tma_load_2d_2cta_hint(smem_b + stage * MM2_B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, leader_full,
-                                  n0 + i * 64, kb * MM_BK, pol_b);
+            for (int j = 0; j < 2; ++j)
+              tma_load_tile32_2cta_hint(smem_a + stage * MM_A_STAGE_BYTES + j * (MM_A_STAGE_BYTES / 2), &tmap_a,
+                                        leader_full, kb * 2 + j, m0 >> 5, pol_a);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              tma_load_tile32_2cta_hint(smem_b + stage * MM2_B_STAGE_BYTES + i * (MM_B_BOX_BYTES / 2), &tmap_b,
+                                        leader_full, (n0 >> 5) + i, kb * 2, pol_b);
+          } else {
+            tma_load_2d_2cta_hint(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, leader_full, kb * MM_BK, m0, pol_a);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              tma_load_2d_2cta_hint(smem_b + stage * MM2_B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, leader_full,
+                                    n0 + i * 64, kb * MM_BK, pol_b);
+          }
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -458,8 +504,9 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
             const uint32_t b_addr = smem_u32(smem_b + stage * MM2_B_STAGE_BYTES);
 #pragma unroll
             for (int k = 0; k < MM_BK / MM_UMMA_K; ++k) {
-              const uint64_t a_desc = umma_smem_desc_sw128(a_addr + k * (MM_UMMA_K * 2), 16, 1024);
-              const uint64_t b_desc = umma_smem_desc_sw128(b_addr + k * (MM_UMMA_K * 128), MM_B_BOX_BYTES, 1024);
+              const uint64_t a_desc = umma_smem_desc(a_addr + (k >> 1) * p.a_khalf + (k & 1) * (MM_UMMA_K * 2), 16,
+                                                     p.a_sbo, p.swz);
+              const uint64_t b_desc = umma_smem_desc(b_addr + k * p.b_kstep, p.b_lbo, p.b_sbo, p.swz);
               umma_ss_2cta(d_tmem, a_desc, b_desc, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
             // release this ring slot in both CTAs once the MMAs above have read it
@@ -531,15 +578,45 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
 // ---------------------------------------------------------------------------------------------
 // Host launcher
 // ---------------------------------------------------------------------------------------------
+// Tensor maps of A, B and C.  Row-major: boxes of 128 x 64, 64 x 64 and 32 x 64 elements, 128-byte swizzle.
+// Tile-major: boxes of 128 x 32, 64 x 32 and 32 x 32 elements (one tile column), 64-byte swizzle.
+static void set_operand_images(MatmulParams* p, int tile32) {
+  if (tile32) {
+    p->swz = UMMA_LAYOUT_SW64;
+    p->a_sbo = 512;                     // 8 rows of 64 bytes
+    p->a_khalf = MM_A_STAGE_BYTES / 2;  // k = 32..63 live in the second 128 x 32 half
+    p->b_lbo = MM_B_BOX_BYTES / 2;      // next 32-column chunk of N = next 4 KB box
+    p->b_sbo = 512;                     // next group of 8 k-rows
+    p->b_kstep = MM_UMMA_K * 64;        // 16 k-rows of 64 bytes
+  } else {
+    p->swz = UMMA_LAYOUT_SW128;
+    p->a_sbo = 1024;                    // 8 rows of 128 bytes
+    p->a_khalf = 2 * MM_UMMA_K * 2;     // one row holds all 64 k: k-steps advance by 32 bytes
+    p->b_lbo = MM_B_BOX_BYTES;          // next 64-column chunk of N = next 8 KB box
+    p->b_sbo = 1024;                    // next group of 8 k-rows
+    p->b_kstep = MM_UMMA_K * 128;       // 16 k-rows of 128 bytes
+  }
+}
+
+static int make_operand_tmaps(const MatmulArgs& a, CUtensorMap* ta, CUtensorMap* tb, CUtensorMap* tc) {
+  int rc;
+  if (a.tile32) {
+    if ((rc = make_tmap_tile32(ta, a.A, a.K, a.M, MM_BM)) != 0) return rc;
+    if ((rc = make_tmap_tile32(tb, a.B, a.N, a.K, MM_BK)) != 0) return rc;
+    return make_tmap_tile32(tc, a.C, a.N, a.M, 32);
+  }
+  if ((rc = make_tmap_bf16_2d(ta, a.A, a.K, a.M, a.lda, 64, MM_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(tb, a.B, a.N, a.K, a.ldb, 64, MM_BK)) != 0) return rc;
+  return make_tmap_bf16_2d(tc, a.C, a.N, a.M, a.ldc, 64, 32);
+}
+
 template <int BN, int STAGES>
 static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_t stream, uint32_t* status) {
   using L = MatmulSmem<BN, STAGES>;
   static_assert(L::TOTAL <= 232448, "shared memory budget exceeded");
   CUtensorMap ta, tb, tc;
   int rc;
-  if ((rc = make_tmap_bf16_2d(&ta, a.A, a.K, a.M, a.lda, 64, MM_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tb, a.B, a.N, a.K, a.ldb, 64, MM_BK)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tc, a.C, a.N, a.M, a.ldc, 64, 32)) != 0) return rc;
+  if ((rc = make_operand_tmaps(a, &ta, &tb, &tc)) != 0) return rc;
 
   MatmulParams p;
   p.M = a.M; p.N = a.N; p.K = a.K;
@@ -554,15 +631,10 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   p.ldbias = a.ldbias;
   p.act = a.act;
   p.round_before_bias = a.round_before_bias;
-  p.b_lbo = 64 * MM_BK * 2;  // next 64-column chunk of N = next 8 KB box
-  p.b_sbo = 1024;            // next group of 8 k-rows
-  p.b_kstep = MM_UMMA_K * 128;  // 16 k-rows of 128 bytes
-  if (const char* dbg = getenv("B200K_DEBUG_BDESC")) {  // bring-up aid: "lbo,sbo,kstep" in bytes
-    unsigned l = 0, sb = 0, ks = 0;
-    if (sscanf(dbg, "%u,%u,%u", &l, &sb, &ks) == 3) { p.b_lbo = l; p.b_sbo = sb; p.b_kstep = ks; }
-  }
+  set_operand_images(&p, a.tile32);
   p.l2_hint = 0;
   p.f16 = a.dtype;
+  p.tile32 = a.tile32;
   p.idesc = umma_idesc_16bit_f32(MM_BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
   p.status = status;
 
@@ -582,9 +654,7 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   static_assert(L::TOTAL <= 232448, "shared memory budget exceeded");
   CUtensorMap ta, tb, tc;
   int rc;
-  if ((rc = make_tmap_bf16_2d(&ta, a.A, a.K, a.M, a.lda, 64, MM_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tb, a.B, a.N, a.K, a.ldb, 64, MM_BK)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tc, a.C, a.N, a.M, a.ldc, 64, 32)) != 0) return rc;
+  if ((rc = make_operand_tmaps(a, &ta, &tb, &tc)) != 0) return rc;
 
   MatmulParams p;
   p.M = a.M; p.N = a.N; p.K = a.K;
@@ -599,8 +669,9 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   p.ldbias = a.ldbias;
   p.act = a.act;
   p.round_before_bias = a.round_before_bias;
-  p.b_lbo = p.b_sbo = p.b_kstep = 0;  // fixed in the kernel
+  set_operand_images(&p, a.tile32);
   p.f16 = a.dtype;
+  p.tile32 = a.tile32;
   p.idesc = umma_idesc_16bit_f32(256, MM2_BN, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
   p.l2_hint = 2;  // keep the group's A row panel in L2 (measured +2 % at 8192^3 over no hint; B evict_first loses)
   if (const char* h = getenv("B200K_MATMUL_L2_HINT")) p.l2_hint = atoi(h);
@@ -619,10 +690,16 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
 int matmul_bf16(const MatmulArgs& a, cudaStream_t stream, uint32_t* status_override) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) return set_error(B200K_ERR_INVALID_ARG, "matmul: M, N, K must be positive (got %d, %d, %d)", a.M, a.N, a.K);
   if (a.A == nullptr || a.B == nullptr || a.C == nullptr) return set_error(B200K_ERR_INVALID_ARG, "matmul: null operand pointer");
-  if (a.lda < a.K || a.ldb < a.N || a.ldc < a.N) return set_error(B200K_ERR_INVALID_ARG, "matmul: leading dimension smaller than the row length");
-  if ((a.lda & 7) || (a.ldb & 7) || (a.ldc & 7))
-    return set_error(B200K_ERR_INVALID_ARG, "matmul: lda/ldb/ldc must be multiples of 8 elements (16-byte rows for TMA); got %lld, %lld, %lld",
-                     (long long)a.lda, (long long)a.ldb, (long long)a.ldc);
+  if (a.tile32) {
+    if ((a.M & 31) || (a.N & 31) || (a.K & 31))
+      return set_error(B200K_ERR_INVALID_ARG, "matmul: tile-major operands need M, N, K multiples of 32 (got %d, %d, %d)", a.M, a.N, a.K);
+    if (a.bias_kind != B200K_BIAS_NONE) return set_error(B200K_ERR_INVALID_ARG, "matmul: tile-major operands take no bias");
+  } else {
+    if (a.lda < a.K || a.ldb < a.N || a.ldc < a.N) return set_error(B200K_ERR_INVALID_ARG, "matmul: leading dimension smaller than the row length");
+    if ((a.lda & 7) || (a.ldb & 7) || (a.ldc & 7))
+      return set_error(B200K_ERR_INVALID_ARG, "matmul: lda/ldb/ldc must be multiples of 8 elements (16-byte rows for TMA); got %lld, %lld, %lld",
+                       (long long)a.lda, (long long)a.ldb, (long long)a.ldc);
+  }
   if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) | reinterpret_cast<uintptr_t>(a.C)) & 15u)
     return set_error(B200K_ERR_INVALID_ARG, "matmul: A, B and C must be 16-byte aligned");
   if (a.bias_kind < B200K_BIAS_NONE || a.bias_kind > B200K_BIAS_FULL_BF16) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad bias_kind %d", a.bias_kind);

@@ -111,6 +111,26 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// Tile-major ("tilized") operands: the matrix is stored as contiguous 32 x 32 element tiles, tiles in
+// row-major order.  Its tensor map has four dimensions (column in tile, tile column, row in tile,
+// tile row) and a box {32, 1, 32, by}: 32*by rows of 32 elements (64 bytes), which with the 64-byte
+// swizzle land densely in shared memory as the canonical 64-byte-swizzled operand image.  (A box
+// that spans two tile columns does not give 128-byte rows under a swizzle mode: TMA pads every
+// 64-byte inner row to the swizzle span.)  Coordinates are in tiles; the innermost coordinate is
+// always 0, which keeps the 16-byte alignment rule of TMA trivially.
+__device__ __forceinline__ void tma_load_tile32(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int tile_x,
+                                                int tile_y) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %3, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(0), "r"(tile_x),
+        "r"(tile_y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_tile32(const CUtensorMap* m, const void* smem_src, int tile_x, int tile_y) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %2, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(0), "r"(tile_x), "r"(tile_y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
@@ -141,7 +161,7 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 // ---------------------------------------------------------------------------------------------
 // tcgen05: descriptors
 // ---------------------------------------------------------------------------------------------
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// Shared-memory matrix descriptor, descriptor version 1 (layout type 2 = 128-byte swizzle, 4 = 64-byte swizzle).
 //   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
 //   bits [32,46) stride byte offset >> 4   bits [46,48) version = 1      bits [61,64) layout type
 // K-major operand (rows of 64 bf16 = 128 B, 8-row groups of 1024 B):
@@ -149,15 +169,22 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 // MN-major operand (rows along K, each 64 bf16 of the M/N extent = 128 B; 8 K-rows = 1024 B):
 //   LBO = byte distance between consecutive 64-element chunks of the M/N extent,
 //   SBO = byte distance between consecutive groups of 8 K-rows (1024 B when rows are packed).
-__host__ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                                   uint32_t sbo_bytes) {
+// With the 64-byte swizzle the same holds with rows of 32 elements (64 B) and 8-row groups of 512 B.
+constexpr uint32_t UMMA_LAYOUT_SW128 = 2;  // 128-byte swizzle: 8-row groups of 128-byte rows (1024 B)
+constexpr uint32_t UMMA_LAYOUT_SW64 = 4;   // 64-byte swizzle: 8-row groups of 64-byte rows (512 B)
+__host__ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                            uint32_t layout_type) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;  // descriptor version (Blackwell)
-  d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+  d |= static_cast<uint64_t>(layout_type & 7u) << 61;
   return d;
+}
+__host__ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                                   uint32_t sbo_bytes) {
+  return umma_smem_desc(smem_addr, lbo_bytes, sbo_bytes, UMMA_LAYOUT_SW128);
 }
 
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
@@ -305,6 +332,17 @@ __device__ __forceinline__ void tma_load_2d_2cta_hint(void* smem_dst, const CUte
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
       " [%0], [%1, {%3, %4}], [%2], %5;"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+// Tile-major operand (see tma_load_tile32) loaded by one CTA of a pair, counted on the leader's barrier.
+__device__ __forceinline__ void tma_load_tile32_2cta_hint(void* smem_dst, const CUtensorMap* m,
+                                                          uint32_t bar_cluster_addr, int tile_x, int tile_y,
+                                                          uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %3, %5}], [%2], %6;"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(0), "r"(tile_x),
+        "r"(tile_y), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {

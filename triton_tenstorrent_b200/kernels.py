@@ -5,6 +5,8 @@
     matmul_kernel_tma[grid](a_desc, b_desc, c_desc, M, N, K, FP8_OUTPUT=..., WARP_SPECIALIZE=...)
                                                                                  09-persistent-matmul.ttnn.py:167-172
     matmul_kernel_fused[grid](a_desc, b_desc, c_desc, bias_desc, M, N, K, ...)   09-matmul-fused.py:175-180
+    matmul_kernel[grid](a, b, c, M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0),
+                        c.stride(1), ACTIVATION=...)                             03-matrix-multiplication.py:413-420
     _attn_fwd[grid](sm_scale, M, Z, H, desc_q, desc_k, desc_v, desc_o, N_CTX=..., HEAD_DIM=...,
                     FP8_OUTPUT=..., STAGE=..., warp_specialize=..., IS_HOPPER=...) 06-fused-attention.py:257-267
 
@@ -119,6 +121,36 @@ matmul_kernel_fused = Kernel(
     ["a_desc", "b_desc", "c_desc", "bias_desc", "M", "N", "K", "BLOCK_SIZE_M", "BLOCK_SIZE_N", "BLOCK_SIZE_K",
      "GROUP_SIZE_M", "FP8_OUTPUT", "WARP_SPECIALIZE"],
     ["tensordesc"] * 4 + ["i32", "i32", "i32"] + ["constexpr"] * 6, _MATMUL_META, spec_fn=_matmul_spec)
+
+_ACTIVATION_CODES = {"": 0, "none": 0, "relu": 1, "leaky_relu": 2}
+
+
+def _matmul_ptr_spec(bound):
+    """ACTIVATION and the operand type are compile-time properties of the reference kernel; LAYOUT says whether
+    the buffers are row-major ("row", the strides apply) or tile-major as the reference kernel addresses them
+    ("tile32", the strides are ignored exactly as examples/matmul/03-matrix-multiplication.py:333-386 ignores them)."""
+    act = bound["ACTIVATION"]
+    if act not in _ACTIVATION_CODES:
+        raise ValueError(f"matmul_kernel: unknown ACTIVATION {act!r}")
+    layout = bound["LAYOUT"]
+    if layout not in ("row", "tile32"):
+        raise ValueError(f"matmul_kernel: unknown LAYOUT {layout!r}")
+    a, b, c = bound["a_ptr"], bound["b_ptr"], bound["c_ptr"]
+    if not (a.dtype == b.dtype == c.dtype) or a.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("matmul_kernel: a, b, c must share one 16-bit float type")
+    if layout == "tile32" and not (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()):
+        raise ValueError("matmul_kernel: tile-major buffers must be contiguous")
+    return [f"ACTIVATION={_ACTIVATION_CODES[act]}", f"F16={1 if a.dtype == torch.float16 else 0}",
+            f"TILE32={1 if layout == 'tile32' else 0}"]
+
+
+matmul_kernel = Kernel(
+    "matmul_kernel",
+    ["a_ptr", "b_ptr", "c_ptr", "M", "N", "K", "stride_am", "stride_ak", "stride_bk", "stride_bn", "stride_cm",
+     "stride_cn", "BLOCK_SIZE_M", "BLOCK_SIZE_N", "BLOCK_SIZE_K", "GROUP_SIZE_M", "ACTIVATION", "LAYOUT"],
+    ["*fp16", "*fp16", "*fp16"] + ["i32"] * 9 + ["constexpr"] * 6,
+    {"BLOCK_SIZE_M": 128, "BLOCK_SIZE_N": 256, "BLOCK_SIZE_K": 64, "GROUP_SIZE_M": 8, "ACTIVATION": "", "LAYOUT": "row"},
+    spec_keys=("BLOCK_SIZE_M", "BLOCK_SIZE_N"), spec_fn=_matmul_ptr_spec)
 
 _attn_fwd = Kernel(
     "_attn_fwd",

@@ -12,7 +12,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["add", "sin", "mul_add", "matmul", "matmul_tma", "matmul_fused", "matmul_tma_fused", "attention",
+__all__ = ["add", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_fused", "matmul_tma_fused", "attention",
            "attention_with_lse", "device_status"]
 
 
@@ -222,13 +222,63 @@ def _host_pipeline_applies(a, b, out, bias=None) -> bool:
             and a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16))
 
 
-def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "") -> torch.Tensor:
+def tilize(t: torch.Tensor, tile: int = 32) -> torch.Tensor:
+    """Row-major [R,S] -> a tensor of the same shape whose MEMORY holds contiguous tile x tile tiles, tiles in
+    row-major order: the layout the reference's matmul_kernel addresses
+    (examples/matmul/03-matrix-multiplication.py:333-344).  A layout helper in torch, not a kernel of this library."""
+    R, S = t.shape
+    if R % tile or S % tile:
+        raise ValueError(f"tilize: shape {tuple(t.shape)} is not a whole number of {tile}x{tile} tiles")
+    return t.reshape(R // tile, tile, S // tile, tile).permute(0, 2, 1, 3).contiguous().view(R, S)
+
+
+def untilize(t: torch.Tensor, tile: int = 32) -> torch.Tensor:
+    """Inverse of tilize: tile-major memory -> row-major."""
+    R, S = t.shape
+    if R % tile or S % tile:
+        raise ValueError(f"untilize: shape {tuple(t.shape)} is not a whole number of {tile}x{tile} tiles")
+    return t.reshape(R // tile, S // tile, tile, tile).permute(0, 2, 1, 3).contiguous().view(R, S)
+
+
+def _matmul_tile32_call(a, b, act, c=None):
+    """A, B, C are [M,K], [K,N], [M,N] tensors whose memory is tile-major (32 x 32 tiles)."""
+    assert a.shape[1] == b.shape[0], "Incompatible dimensions"
+    assert a.dtype == b.dtype, "Incompatible dtypes"
+    lib = _lib.load()
+    ad, bd = _to_device(a), _to_device(b)
+    for name, t in (("a", ad), ("b", bd)):
+        if t.dim() != 2 or t.dtype not in (torch.bfloat16, torch.float16):
+            raise TypeError(f"{name}: 2-D bf16 or fp16 tensor expected")
+        if not t.is_contiguous() or t.data_ptr() % 16 != 0:
+            raise ValueError(f"{name}: a tile-major buffer must be contiguous and 16-byte aligned")
+    M, K = ad.shape
+    _, N = bd.shape
+    if M % 32 or N % 32 or K % 32:
+        raise ValueError(f"matmul: tile-major operands need M, N, K multiples of 32; got {M}, {N}, {K}")
+    if c is None:
+        c = torch.empty((M, N), device=ad.device, dtype=ad.dtype)
+    elif (tuple(c.shape) != (M, N) or c.dtype != ad.dtype or not c.is_cuda or c.device != ad.device
+          or not c.is_contiguous() or c.data_ptr() % 16 != 0):
+        raise ValueError(f"matmul: the tile-major output must be a contiguous {ad.dtype} [{M},{N}] tensor on {ad.device}")
+    with torch.cuda.device(ad.device):
+        _lib.check(lib.b200k_matmul_tile32(ad.data_ptr(), bd.data_ptr(), c.data_ptr(), M, N, K, act,
+                                           1 if ad.dtype == torch.float16 else 0, _stream()))
+    return c
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, activation: str = "", layout: str = "row") -> torch.Tensor:
     """C = act(A.B) with act in {"", "leaky_relu", "relu"} applied to the fp32 accumulator.
-    Mirrors matmul(a, b, activation), examples/matmul/03-matrix-multiplication.py:403-421 (operands are plain
-    row-major here; the 32x32 tile-major addressing of that file is a Tenstorrent memory layout)."""
+    Mirrors matmul(a, b, activation), examples/matmul/03-matrix-multiplication.py:403-421.
+    layout="row": a, b and the result are ordinary row-major tensors.
+    layout="tile32": the memory of a, b and of the result is tile-major (contiguous 32 x 32 tiles), which is how the
+    reference kernel addresses its buffers (:333-386); see tilize / untilize."""
     assert a.is_contiguous(), "Matrix A must be contiguous"
     if activation not in _ACTIVATIONS:
         raise ValueError(f"unknown activation {activation!r}")
+    if layout == "tile32":
+        return _like_input(_matmul_tile32_call(a, b, _ACTIVATIONS[activation]), a)
+    if layout != "row":
+        raise ValueError(f"unknown layout {layout!r} (expected 'row' or 'tile32')")
     return _like_input(_matmul_call(a, b, act=_ACTIVATIONS[activation]), a)
 
 
