@@ -14,6 +14,11 @@
 // (cpu/lib/Dialect/TritonCPU/Transforms/MakePersistentKernel.cpp:144-198).
 // Contraction semantics follow matmul_kernel_tma (.ttnn.py:126-143): zero fill outside [M,K]/[K,N],
 // fp32 accumulation, one RNE downcast, stores outside [M,N] dropped.
+//
+// Operands may also be stored tile-major (contiguous 32 x 32 tiles), the layout the reference's
+// pointer-based matmul_kernel addresses (examples/matmul/03-matrix-multiplication.py:333-386): the
+// same kernels then fetch boxes of one tile column through 4-D tensor maps into 64-byte-swizzled
+// operand images; only tensor maps, boxes per stage and descriptor constants differ.
 #include <stdio.h>
 #include <stdlib.h>
 

@@ -8,6 +8,8 @@ result is copied back, which is what the reference's D2M launcher does on every 
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 from . import _lib
@@ -18,6 +20,16 @@ __all__ = ["add", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma"
 
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+_NO_SWITCH = contextlib.nullcontext()
+
+
+def _on(device):
+    """Context that makes `device` current for a C-ABI call; free when it already is (the usual case)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
 
 
 def _require_cuda():
@@ -66,7 +78,7 @@ def add(x: torch.Tensor, y: torch.Tensor, BLOCK_SIZE: int = 1024) -> torch.Tenso
     lib = _lib.load()
     xd, yd = _to_device(x).contiguous(), _to_device(y).contiguous()
     out = torch.empty_like(xd)
-    with torch.cuda.device(xd.device):
+    with _on(xd.device):
         _lib.check(lib.b200k_add_f32(xd.data_ptr(), yd.data_ptr(), out.data_ptr(), out.numel(), BLOCK_SIZE, _stream()))
     return _like_input(out, x)
 
@@ -77,7 +89,7 @@ def sin(x: torch.Tensor, BLOCK_SIZE: int = 1024) -> torch.Tensor:
     lib = _lib.load()
     xd = _to_device(x).contiguous()
     out = torch.empty_like(xd)
-    with torch.cuda.device(xd.device):
+    with _on(xd.device):
         _lib.check(lib.b200k_sin_f32(xd.data_ptr(), out.data_ptr(), out.numel(), BLOCK_SIZE, _stream()))
     return _like_input(out, x)
 
@@ -88,7 +100,7 @@ def mul_add(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, BLOCK_SIZE: int =
     lib = _lib.load()
     xd, yd, zd = (_to_device(t).contiguous() for t in (x, y, z))
     out = torch.empty_like(xd)
-    with torch.cuda.device(xd.device):
+    with _on(xd.device):
         _lib.check(lib.b200k_mul_add_f32(xd.data_ptr(), yd.data_ptr(), zd.data_ptr(), out.data_ptr(), out.numel(),
                                          BLOCK_SIZE, _stream()))
     return _like_input(out, x)
@@ -199,7 +211,7 @@ def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT
             bias = bias.contiguous()
         bias_ptr, ldbias = bias.data_ptr(), bias.stride(0)
     entry = lib.b200k_matmul_f16 if dtype == torch.float16 else lib.b200k_matmul_bf16
-    with torch.cuda.device(ad.device):
+    with _on(ad.device):
         _lib.check(entry(ad.data_ptr(), bd.data_ptr(), c.data_ptr(), M, N, K, ad.stride(0), bd.stride(0),
                          c.stride(0), bias_ptr, bias_kind, ldbias, act, round_before_bias, _stream()))
     return c
@@ -260,7 +272,7 @@ def _matmul_tile32_call(a, b, act, c=None):
     elif (tuple(c.shape) != (M, N) or c.dtype != ad.dtype or not c.is_cuda or c.device != ad.device
           or not c.is_contiguous() or c.data_ptr() % 16 != 0):
         raise ValueError(f"matmul: the tile-major output must be a contiguous {ad.dtype} [{M},{N}] tensor on {ad.device}")
-    with torch.cuda.device(ad.device):
+    with _on(ad.device):
         _lib.check(lib.b200k_matmul_tile32(ad.data_ptr(), bd.data_ptr(), c.data_ptr(), M, N, K, act,
                                            1 if ad.dtype == torch.float16 else 0, _stream()))
     return c
@@ -321,7 +333,7 @@ def attention_with_lse(q, k, v, causal, sm_scale, warp_specialize: bool = True):
     qd, kd, vd = (_to_device(t).contiguous() for t in (q, k, v))
     o = torch.empty_like(qd)
     M = torch.empty((Z, H, N_CTX), device=qd.device, dtype=torch.float32)
-    with torch.cuda.device(qd.device):
+    with _on(qd.device):
         _lib.check(lib.b200k_attn_fwd_bf16(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), M.data_ptr(),
                                            Z, H, N_CTX, D, 1 if causal else 0, float(sm_scale), _stream()))
     return _like_input(o, q), _like_input(M, q)
