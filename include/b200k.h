@@ -51,6 +51,15 @@ const char* b200k_last_error(void);
 int b200k_add_f32(const float* x, const float* y, float* out, int64_t n, int block, void* stream);
 
 /*
+ * out[i] = x[i] + y[i] on bf16 tensors: the exact sum rounded once to nearest even.
+ * Replaces: add_kernel of python/tutorials/01-vector-add.loop.py:29-66, which that tutorial runs on
+ * bf16 tensors (:102-103).  Its row_count loop (each program walks row_count consecutive blocks) is a
+ * work partition, not arithmetic: through b200k_launch the kernel "add_kernel" accepts the extra
+ * row_count argument and checks that grid * row_count * BLOCK_SIZE covers n.
+ */
+int b200k_add_bf16(const void* x, const void* y, void* out, int64_t n, int block, void* stream);
+
+/*
  * out[i] = sinf(x[i]), fp32 (CUDA precise sinf, <= 1 ulp).
  * Replaces: sin_kernel, examples/01-sin-kernel.py:17-29 (launch :36).
  */

@@ -46,6 +46,7 @@ def load() -> ctypes.CDLL:
     lib.oracle_set_threads.restype = None
     lib.oracle_block_range.argtypes = [c_int64, c_int, c_int, POINTER(c_int64), POINTER(c_int64)]
     lib.oracle_add_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int]
+    lib.oracle_add_loop.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int]
     lib.oracle_sin_f32.argtypes = [c_void_p, c_void_p, c_int64, c_int, c_int]
     lib.oracle_sin_f64_to_f32.argtypes = [c_void_p, c_void_p, c_int64]
     lib.oracle_mul_add_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int]
@@ -55,7 +56,7 @@ def load() -> ctypes.CDLL:
     lib.oracle_matmul_kernel_tile32.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int]
     lib.oracle_attn_fwd_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                          c_int, c_float, c_int, c_int]
-    for fn in ("oracle_block_range", "oracle_add_f32", "oracle_sin_f32", "oracle_sin_f64_to_f32", "oracle_mul_add_f32",
+    for fn in ("oracle_block_range", "oracle_add_f32", "oracle_add_loop", "oracle_sin_f32", "oracle_sin_f64_to_f32", "oracle_mul_add_f32",
                "oracle_golden_matmul", "oracle_golden_matmul_naive", "oracle_matmul_kernel_tile32", "oracle_attn_fwd_bf16"):
         getattr(lib, fn).restype = None
     _lib = lib
@@ -90,6 +91,17 @@ def add(x, y, block: int = 1024, workers: int = 0):
     x, y = _cpu(x, torch.float32), _cpu(y, torch.float32)
     out = torch.empty_like(x)
     load().oracle_add_f32(x.data_ptr(), y.data_ptr(), out.data_ptr(), x.numel(), block, workers)
+    return out
+
+
+def add_loop(x, y, row_count: int, grid: int, block: int = 1024, fill: float = 0.0):
+    """The row_count-loop form of add_kernel (python/tutorials/01-vector-add.loop.py:29-66), fp32 or bf16.
+    Elements that no program owns keep `fill`."""
+    assert x.dtype == y.dtype and x.dtype in (torch.float32, torch.bfloat16)
+    x, y = _cpu(x), _cpu(y)
+    out = torch.full_like(x, fill)
+    load().oracle_add_loop(x.data_ptr(), y.data_ptr(), out.data_ptr(), x.numel(), row_count, block, grid,
+                           0 if x.dtype == torch.float32 else 1)
     return out
 
 

@@ -101,6 +101,36 @@ void oracle_add_f32(const float* x, const float* y, float* out, int64_t n, int b
   }
 }
 
+/* add_kernel of python/tutorials/01-vector-add.loop.py:29-66, one program at a time: program pid owns
+ * the element range [pid*BLOCK*row_count, min(+BLOCK*row_count, n)) (:46-48) and walks it in
+ * lrow_count = cdiv(range, BLOCK) rows of BLOCK elements under the mask offsets < n (:49-66); a
+ * program whose range starts at or beyond n does nothing (cdiv of a non-positive length, :49).
+ * Elements no program owns are left untouched.  dtype 0 = fp32, 1 = bf16 bit patterns (the tutorial
+ * runs bf16, :102-103; a bf16 add is the exact sum rounded to nearest even). */
+void oracle_add_loop(const void* xv, const void* yv, void* outv, int64_t n, int64_t row_count, int block, int grid,
+                     int dtype) {
+#pragma omp parallel for schedule(static)
+  for (int pid = 0; pid < grid; ++pid) {
+    int64_t block_start = (int64_t)pid * block * row_count;
+    int64_t block_end = block_start + (int64_t)block * row_count;
+    if (block_end > n) block_end = n;
+    const int64_t block_diff = block_end - block_start;
+    const int64_t lrow_count = block_diff > 0 ? (block_diff + block - 1) / block : 0;
+    for (int64_t idx = 0; idx < lrow_count; ++idx) {
+      for (int64_t i = block_start; i < block_start + block; ++i) {
+        if (i >= n) continue;
+        if (dtype == 0) {
+          ((float*)outv)[i] = ((const float*)xv)[i] + ((const float*)yv)[i];
+        } else {
+          const float sum = bf16_to_f32(((const uint16_t*)xv)[i]) + bf16_to_f32(((const uint16_t*)yv)[i]);
+          ((uint16_t*)outv)[i] = f32_to_bf16(sum);
+        }
+      }
+      block_start += block;
+    }
+  }
+}
+
 /* sin_kernel, examples/01-sin-kernel.py:17-29; tl.sin lowers to llvm.sin.f32, i.e. the C library's
  * sinf, on the reference's CPU path (cpu/lib/TritonCPUToLLVM/TritonCPUToLLVM.cpp:130). */
 void oracle_sin_f32(const float* x, float* out, int64_t n, int block, int workers) {

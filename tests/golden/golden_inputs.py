@@ -14,6 +14,9 @@ import torch
 
 ADD_SIZES = [1, 33, 1024, 5000, 98432]
 SIN_SIZES = [32, 1024, 98432]
+# (n, programs, row_count) of the row_count-loop add_kernel; the first is the tutorial's own launch
+# (n_cores = 130 > 97 rows, so 97 programs of one row each), the last leaves elements uncovered
+ADD_LOOP_CASES = [(98432, 97, 1), (50000, 7, 7), (33333, 3, 11), (50000, 5, 7)]
 MATMUL_SHAPES = [(32, 32, 32), (64, 32, 32), (128, 256, 64), (96, 160, 136), (256, 256, 256)]
 FUSED_SHAPES = [(64, 64, 256), (128, 192, 512)]
 # (M, N, K, ACTIVATION) of the pointer-based matmul_kernel on tile-major fp16 buffers

@@ -17,12 +17,12 @@ No reference file is modified or copied into this repository; only the resulting
 stored.
 
 Outputs (small .npz files, a few hundred KB in total):
-  add.npz, sin.npz, matmul.npz, matmul_fused.npz, attention.npz, matmul_tile32.npz
+  add.npz, add_loop.npz, sin.npz, matmul.npz, matmul_fused.npz, attention.npz, matmul_tile32.npz
 Inputs are regenerated from their seeds by `golden_inputs.py`; each .npz keeps a sha256 of the
 input bytes so that a drift of torch's CPU RNG cannot silently invalidate the vectors.
 
 Run:  REFERENCE_ROOT=<checkout of the reference> python tests/golden/make_golden.py [set ...]
-      (sets: add sin matmul matmul_fused attention matmul_tile32; default all)
+      (sets: add add_loop sin matmul matmul_fused attention matmul_tile32; default all)
 """
 from __future__ import annotations
 
@@ -49,6 +49,7 @@ REF = Path(os.environ["REFERENCE_ROOT"])
 KERNEL_SOURCES = {
     # module name -> (reference file, functions to extract in order)
     "ref_add": ("python/tutorials/01-vector-add.py", ["add_kernel"]),
+    "ref_add_loop": ("python/tutorials/01-vector-add.loop.py", ["add_kernel"]),
     "ref_sin": ("examples/01-sin-kernel.py", ["sin_kernel"]),
     "ref_matmul": ("examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py", ["matmul_kernel_tma"]),
     "ref_fused": ("python/tutorials/09-matmul-fused.py", ["matmul_kernel_fused"]),
@@ -139,6 +140,23 @@ def main():
                 k["ref_add"].add_kernel[((n + 1023) // 1024,)](x, y, o, n, BLOCK_SIZE=1024)
                 out[f"in_sha_{n}"], out[f"out_{n}"] = np.array(gi.digest(x, y)), o.numpy()
             np.savez_compressed(HERE / "add.npz", **out)
+
+        if want("add_loop"):
+            # ---- add_kernel with the row_count loop (python/tutorials/01-vector-add.loop.py:29-66), launched as
+            #      add() does (:89).  fp32 only: the interpreter cannot do bf16 arithmetic.  The output starts as a
+            #      sentinel so that elements no program owns are visible.
+            out = {}
+            for (n, programs, row_count) in gi.ADD_LOOP_CASES:
+                x, y = gi.add_inputs(n, seed=2)
+                o = torch.full_like(x, -7.5)
+                k["ref_add_loop"].add_kernel[(programs,)](x, y, o, n, row_count, BLOCK_SIZE=1024)
+                tag = f"{n}_{programs}_{row_count}"
+                # the op is bit-exact, so a digest of the output pins it as well as the bytes; the full output is
+                # kept for the smallest case only
+                out[f"in_sha_{tag}"], out[f"out_sha_{tag}"] = np.array(gi.digest(x, y)), np.array(gi.digest(o))
+                if n < 40000:
+                    out[f"out_{tag}"] = o.numpy()
+            np.savez_compressed(HERE / "add_loop.npz", **out)
 
         if want("sin"):
             # ---- sin_kernel (examples/01-sin-kernel.py:17-29)

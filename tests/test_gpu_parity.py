@@ -55,6 +55,42 @@ def test_add_oracle_bit_exact_edges(n):
     assert _bits_equal(got, oracle.add(x, y)) if n else got.numel() == 0
 
 
+@pytest.mark.parametrize("case", gi.ADD_LOOP_CASES[:3])
+def test_add_loop_golden_bit_exact(golden_dir, case):
+    # the row_count-loop launch form (python/tutorials/01-vector-add.loop.py:89) against what the reference's
+    # kernel source wrote; fp32 through kernels.add_kernel_loop, then the tutorial's bf16 through ops.add_loop
+    n, programs, row_count = case
+    g = np.load(golden_dir / "add_loop.npz")
+    x, y = gi.add_inputs(n, seed=2)
+    out = torch.full((n,), -7.5, device="cuda")
+    kernels.add_kernel_loop[(programs,)](x.cuda(), y.cuda(), out, n, row_count, BLOCK_SIZE=1024, num_warps=1)
+    assert gi.digest(out.cpu()) == str(g[f"out_sha_{n}_{programs}_{row_count}"])
+    xb, yb = x.bfloat16(), y.bfloat16()
+    got = ops.add_loop(xb.cuda(), yb.cuda()).cpu()
+    assert torch.equal(got.view(torch.int16), oracle.add_loop(xb, yb, -(-(-(-n // 1024)) // 130), 130).view(torch.int16))
+
+
+def test_add_loop_rejects_uncovered_launch():
+    # the reference leaves elements that no program owns untouched; this launcher refuses such a grid
+    n, programs, row_count = gi.ADD_LOOP_CASES[3]
+    x, y = gi.add_inputs(n, seed=2)
+    with pytest.raises(_lib.B200KError) as e:
+        kernels.add_kernel_loop[(programs,)](x.cuda(), y.cuda(), torch.empty(n, device="cuda"), n, row_count, BLOCK_SIZE=1024)
+    assert "does not cover" in str(e.value)
+
+
+@pytest.mark.parametrize("n", [0, 1, 7, 8, 9, 1023, 4099, 98432, (1 << 20) + 5])
+def test_add_bf16_bit_exact(n):
+    # bf16 add == exact sum rounded to nearest even, over the whole exponent range and with unaligned views
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(n + 3, generator=g) * torch.exp2(torch.randint(-20, 20, (n + 3,), generator=g).float())).bfloat16()
+    y = (torch.randn(n + 3, generator=g) * torch.exp2(torch.randint(-20, 20, (n + 3,), generator=g).float())).bfloat16()
+    got = ops.add(x[:n].cuda(), y[:n].cuda()).cpu()
+    assert torch.equal(got.view(torch.int16), (x[:n] + y[:n]).view(torch.int16))
+    got = ops.add(x.cuda()[3:], y.cuda()[1:n + 1]).cpu()          # 6- and 2-byte offsets: scalar path
+    assert torch.equal(got.view(torch.int16), (x[3:] + y[1:n + 1]).view(torch.int16))
+
+
 def test_add_unaligned_views_and_canaries():
     x, y = gi.add_inputs(5003, seed=5)
     xd, yd = x.cuda(), y.cuda()

@@ -35,7 +35,7 @@ def recording(monkeypatch):
     RecordingLauncher.calls = []
     monkeypatch.setattr(driver.active, "launcher_cls", RecordingLauncher)
     monkeypatch.setattr(driver.active, "get_current_stream", lambda device_id=None: 0)
-    for k in (kernels.add_kernel, kernels.sin_kernel, kernels.matmul_kernel_tma, kernels.matmul_kernel_fused,
+    for k in (kernels.add_kernel, kernels.add_kernel_loop, kernels.sin_kernel, kernels.matmul_kernel_tma, kernels.matmul_kernel_fused,
               kernels.matmul_kernel, kernels._attn_fwd):
         monkeypatch.setattr(k, "launcher", None)
     return RecordingLauncher.calls
@@ -54,6 +54,23 @@ def test_add_kernel_launch_surface(recording):
     assert kinds == [_lib.ARG_PTR] * 3 + [_lib.ARG_I32]    # the constexpr BLOCK_SIZE is dropped
     assert call["flat"][3][1] == n
     assert [v for _, v in call["flat"][:3]] == [x.data_ptr(), y.data_ptr(), out.data_ptr()]
+
+
+def test_add_kernel_loop_launch_surface(recording):
+    # add_kernel[grid](x, y, output, n_elements, row_count, BLOCK_SIZE=..., num_warps=1), 01-vector-add.loop.py:89
+    n = 300000
+    x, y, out = (fake(torch.zeros(n, dtype=torch.bfloat16)) for _ in range(3))
+    n_cores, block = 130, 1024
+    n_rows = -(-n // block)
+    row_count = -(-n_rows // n_cores)
+    kernels.add_kernel_loop[lambda meta: (n_cores,)](x, y, out, n, row_count, BLOCK_SIZE=block, num_warps=1)
+    call = recording[0]
+    assert call["grid"] == (130, 1, 1) and row_count == 3
+    assert call["function"] == "add_kernel:BLOCK_SIZE=1024,BF16=1"
+    assert [k for k, _ in call["flat"]] == [_lib.ARG_PTR] * 3 + [_lib.ARG_I32] * 2
+    assert [v for _, v in call["flat"][3:]] == [n, row_count]
+    with pytest.raises(TypeError):
+        kernels.add_kernel_loop[(1,)](x, y, fake(torch.zeros(n)), n, row_count, BLOCK_SIZE=block)   # mixed dtypes
 
 
 def test_descriptor_flattening_matches_reference_order(recording):

@@ -31,6 +31,27 @@ def test_add_bit_exact(golden_dir, n):
         assert np.array_equal(out.numpy(), g[f"out_{n}"])
 
 
+@pytest.mark.parametrize("case", gi.ADD_LOOP_CASES)
+def test_add_loop_bit_exact(golden_dir, case):
+    # the row_count-loop add_kernel (python/tutorials/01-vector-add.loop.py:29-66), including a launch whose
+    # programs do not own every element (those keep the sentinel)
+    n, programs, row_count = case
+    g = np.load(golden_dir / "add_loop.npz")
+    x, y = gi.add_inputs(n, seed=2)
+    tag = f"{n}_{programs}_{row_count}"
+    assert str(g[f"in_sha_{tag}"]) == gi.digest(x, y)
+    out = oracle.add_loop(x, y, row_count, programs, fill=-7.5)
+    assert gi.digest(out) == str(g[f"out_sha_{tag}"])
+    if f"out_{tag}" in g:
+        assert np.array_equal(out.numpy().view(np.uint32), g[f"out_{tag}"].view(np.uint32))
+    covered = min(n, programs * row_count * 1024)
+    assert torch.equal(out[:covered], oracle.add(x, y)[:covered]) and bool((out[covered:] == -7.5).all())
+    # bf16 form (the tutorial's dtype): exact sum rounded to nearest even == torch's bf16 add
+    xb, yb = x.bfloat16(), y.bfloat16()
+    outb = oracle.add_loop(xb, yb, row_count, programs, fill=-7.5)
+    assert torch.equal(outb[:covered].view(torch.int16), (xb + yb)[:covered].view(torch.int16))
+
+
 @pytest.mark.parametrize("n", gi.SIN_SIZES)
 def test_sin_within_2ulp(golden_dir, n):
     g = np.load(golden_dir / "sin.npz")

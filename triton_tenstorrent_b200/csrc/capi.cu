@@ -269,12 +269,24 @@ static int generic_launch(const char* kernel_name, int gx, int gy, int gz, cudaS
     void* p[4] = {nullptr, nullptr, nullptr, nullptr};
     for (int i = 0; i < nptr; ++i) p[i] = c.ptr();
     const int64_t n = c.integer();
+    // add_kernel of python/tutorials/01-vector-add.loop.py:29-35 takes one more scalar: row_count, the
+    // number of consecutive blocks each program walks
+    int64_t row_count = 1;
+    if (name == "add_kernel" && c.i + 1 == nargs) {
+      row_count = c.integer();
+      if (row_count <= 0) return set_error(B200K_ERR_INVALID_ARG, "launch add_kernel: row_count must be positive (got %lld)", (long long)row_count);
+    }
     if (c.fail || c.i != nargs) return set_error(B200K_ERR_INVALID_ARG, "launch %s: expected %d pointers and n_elements, got %d arguments", name.c_str(), nptr, nargs);
     const long block = spec_value(spec, "BLOCK_SIZE", 0);
-    if (block > 0 && static_cast<int64_t>(gx) * block < n)
-      return set_error(B200K_ERR_INVALID_ARG, "launch %s: grid %d x BLOCK_SIZE %ld does not cover n=%lld", name.c_str(), gx, block, (long long)n);
+    if (block > 0 && static_cast<int64_t>(gx) * block * row_count < n)
+      return set_error(B200K_ERR_INVALID_ARG, "launch %s: grid %d x BLOCK_SIZE %ld x row_count %lld does not cover n=%lld", name.c_str(), gx, block, (long long)row_count, (long long)n);
     if (n < 0) return set_error(B200K_ERR_INVALID_ARG, "launch %s: negative n", name.c_str());
-    if (name == "add_kernel") return add_f32((const float*)p[0], (const float*)p[1], (float*)p[2], n, stream);
+    const bool bf16 = spec_value(spec, "BF16", 0) != 0;
+    if (bf16 && name != "add_kernel") return set_error(B200K_ERR_UNSUPPORTED, "launch %s: only add_kernel has a bf16 form", name.c_str());
+    if (name == "add_kernel") {
+      if (bf16) return add_bf16((const uint16_t*)p[0], (const uint16_t*)p[1], (uint16_t*)p[2], n, stream);
+      return add_f32((const float*)p[0], (const float*)p[1], (float*)p[2], n, stream);
+    }
     if (name == "sin_kernel") return sin_f32((const float*)p[0], (float*)p[1], n, stream);
     return mul_add_f32((const float*)p[0], (const float*)p[1], (const float*)p[2], (float*)p[3], n, stream);
   }
@@ -382,6 +394,15 @@ int b200k_add_f32(const float* x, const float* y, float* out, int64_t n, int blo
   if (block <= 0) return set_error(B200K_ERR_INVALID_ARG, "add: BLOCK_SIZE must be positive (got %d)", block);
   if (n > 0 && (x == nullptr || y == nullptr || out == nullptr)) return set_error(B200K_ERR_INVALID_ARG, "add: null pointer");
   return add_f32(x, y, out, n, static_cast<cudaStream_t>(stream));
+}
+
+int b200k_add_bf16(const void* x, const void* y, void* out, int64_t n, int block, void* stream) {
+  clear_error();
+  if (n < 0) return set_error(B200K_ERR_INVALID_ARG, "add: n must be >= 0 (got %lld)", (long long)n);
+  if (block <= 0) return set_error(B200K_ERR_INVALID_ARG, "add: BLOCK_SIZE must be positive (got %d)", block);
+  if (n > 0 && (x == nullptr || y == nullptr || out == nullptr)) return set_error(B200K_ERR_INVALID_ARG, "add: null pointer");
+  return add_bf16(static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(y), static_cast<uint16_t*>(out), n,
+                  static_cast<cudaStream_t>(stream));
 }
 
 int b200k_sin_f32(const float* x, float* out, int64_t n, int block, void* stream) {

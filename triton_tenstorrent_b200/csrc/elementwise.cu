@@ -7,7 +7,12 @@
 //   add      python/tutorials/01-vector-add.py:47-54     out = x + y          (one IEEE fp32 add)
 //   sin      examples/01-sin-kernel.py:25-29              out = sin(x)         (precise sinf, <= 1 ulp)
 //   mul_add  python/tutorials/01-vector-mul-add.py        out = x * y + z      (two roundings, no FMA)
+//   add bf16 python/tutorials/01-vector-add.loop.py:29-66 (run on bf16 tensors, :102-103): the exact sum
+//            rounded once to nearest even; computed as an fp32 add of the widened operands and one
+//            RNE downcast, which gives the same bits (the fp32 sum of two bf16 values can only be
+//            inexact when the smaller operand is far below half a bf16 ulp of the larger)
 #include "launch.h"
+#include "ptx.cuh"
 
 namespace b200k {
 
@@ -126,6 +131,76 @@ static int ew_launch(const float* x, const float* y, const float* z, float* out,
     ew_scalar_kernel<OP><<<grid, EW_THREADS, 0, stream>>>(x, y, z, out, done, n);
     count_launch();
     B200K_CHECK_LAUNCH("elementwise scalar kernel");
+  }
+  return B200K_OK;
+}
+
+// ---- bf16 add: 8 elements per 128-bit access, same tiling as the fp32 kernels
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
+  return pack_bf16x2(bf16_bits_to_f32(a & 0xFFFFu) + bf16_bits_to_f32(b & 0xFFFFu),
+                     bf16_bits_to_f32(a >> 16) + bf16_bits_to_f32(b >> 16));
+}
+
+__global__ void __launch_bounds__(EW_THREADS) ew_add_bf16_vec8_kernel(const uint4* __restrict__ x,
+                                                                      const uint4* __restrict__ y,
+                                                                      uint4* __restrict__ out, int64_t n8) {
+  const int64_t tile = static_cast<int64_t>(EW_THREADS) * EW_UNROLL;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * tile;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < n8; base += stride) {
+    uint4 xv[EW_UNROLL], yv[EW_UNROLL];
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t i = base + threadIdx.x + static_cast<int64_t>(u) * EW_THREADS;
+      if (i < n8) {
+        xv[u] = __ldcs(x + i);
+        yv[u] = __ldcs(y + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      const int64_t i = base + threadIdx.x + static_cast<int64_t>(u) * EW_THREADS;
+      if (i < n8)
+        __stcs(out + i, make_uint4(add_bf16x2(xv[u].x, yv[u].x), add_bf16x2(xv[u].y, yv[u].y),
+                                   add_bf16x2(xv[u].z, yv[u].z), add_bf16x2(xv[u].w, yv[u].w)));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(EW_THREADS) ew_add_bf16_scalar_kernel(const uint16_t* __restrict__ x,
+                                                                        const uint16_t* __restrict__ y,
+                                                                        uint16_t* __restrict__ out, int64_t begin,
+                                                                        int64_t n) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    out[i] = static_cast<uint16_t>(pack_bf16x2(bf16_bits_to_f32(x[i]) + bf16_bits_to_f32(y[i]), 0.f) & 0xFFFFu);
+}
+
+int add_bf16(const uint16_t* x, const uint16_t* y, uint16_t* out, int64_t n, cudaStream_t stream) {
+  if (n == 0) return B200K_OK;
+  const DeviceInfo* dev = current_device_info();
+  if (dev == nullptr) return B200K_ERR_NO_DEVICE;
+  const bool vec_ok = aligned16(x) && aligned16(y) && aligned16(out);
+  const int64_t n8 = vec_ok ? (n / 8) : 0;
+  if (n8 > 0) {
+    const int64_t tile = static_cast<int64_t>(EW_THREADS) * EW_UNROLL;
+    const int64_t want = (n8 + tile - 1) / tile;
+    const int64_t cap = static_cast<int64_t>(dev->sm_count) * B200K_EW_CTAS_PER_SM;
+    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+    ew_add_bf16_vec8_kernel<<<grid, EW_THREADS, 0, stream>>>(reinterpret_cast<const uint4*>(x),
+                                                             reinterpret_cast<const uint4*>(y),
+                                                             reinterpret_cast<uint4*>(out), n8);
+    count_launch();
+    B200K_CHECK_LAUNCH("bf16 add vec8 kernel");
+  }
+  const int64_t done = n8 * 8;
+  if (done < n) {
+    const int64_t rest = n - done;
+    const int64_t want = (rest + EW_THREADS - 1) / EW_THREADS;
+    const int64_t cap = static_cast<int64_t>(dev->sm_count) * 8;
+    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+    ew_add_bf16_scalar_kernel<<<grid, EW_THREADS, 0, stream>>>(x, y, out, done, n);
+    count_launch();
+    B200K_CHECK_LAUNCH("bf16 add scalar kernel");
   }
   return B200K_OK;
 }

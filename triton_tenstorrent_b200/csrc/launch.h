@@ -50,6 +50,7 @@ int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t
 
 // Kernel launchers (one translation unit each).
 int add_f32(const float* x, const float* y, float* out, int64_t n, cudaStream_t s);
+int add_bf16(const uint16_t* x, const uint16_t* y, uint16_t* out, int64_t n, cudaStream_t s);
 int sin_f32(const float* x, float* out, int64_t n, cudaStream_t s);
 int mul_add_f32(const float* x, const float* y, const float* z, float* out, int64_t n, cudaStream_t s);
 

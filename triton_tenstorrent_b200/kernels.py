@@ -1,6 +1,7 @@
 """The example kernels as launchable objects with the reference's call syntax:
 
     add_kernel[grid](x, y, output, n_elements, BLOCK_SIZE=1024)                  01-vector-add.py:75
+    add_kernel_loop[grid](x, y, output, n_elements, row_count, BLOCK_SIZE=1024)  01-vector-add.loop.py:89
     sin_kernel[grid](x, output, n_elements, BLOCK_SIZE=1024)                     01-sin-kernel.py:36
     matmul_kernel_tma[grid](a_desc, b_desc, c_desc, M, N, K, FP8_OUTPUT=..., WARP_SPECIALIZE=...)
                                                                                  09-persistent-matmul.ttnn.py:167-172
@@ -89,9 +90,23 @@ class Kernel:
                       launch_exit_hook, *[bound[n] for n in self.arg_names])
 
 
+def _add_spec(bound):
+    """The element type is a compile-time property of the reference kernel (fp32 in 01-vector-add.py, bf16 in
+    01-vector-add.loop.py:102-103); here it travels in the name."""
+    dt = bound["x_ptr"].dtype
+    if dt != bound["y_ptr"].dtype or dt != bound["output_ptr"].dtype or dt not in (torch.float32, torch.bfloat16):
+        raise TypeError("add_kernel: x, y and output must all be fp32 or all bf16")
+    return ["BF16=1"] if dt == torch.bfloat16 else []
+
+
 add_kernel = Kernel(
     "add_kernel", ["x_ptr", "y_ptr", "output_ptr", "n_elements", "BLOCK_SIZE"],
-    ["*fp32", "*fp32", "*fp32", "i32", "constexpr"], {}, spec_keys=("BLOCK_SIZE",))
+    ["*fp32", "*fp32", "*fp32", "i32", "constexpr"], {}, spec_keys=("BLOCK_SIZE",), spec_fn=_add_spec)
+
+# add_kernel of python/tutorials/01-vector-add.loop.py:29-35: one more scalar, row_count (launch :89)
+add_kernel_loop = Kernel(
+    "add_kernel", ["x_ptr", "y_ptr", "output_ptr", "n_elements", "row_count", "BLOCK_SIZE"],
+    ["*fp32", "*fp32", "*fp32", "i32", "i32", "constexpr"], {}, spec_keys=("BLOCK_SIZE",), spec_fn=_add_spec)
 
 sin_kernel = Kernel(
     "sin_kernel", ["x_ptr", "output_ptr", "n_elements", "BLOCK_SIZE"],

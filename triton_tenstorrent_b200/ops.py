@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["add", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_fused", "matmul_tma_fused", "attention",
+__all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_fused", "matmul_tma_fused", "attention",
            "attention_with_lse", "device_status"]
 
 
@@ -61,11 +61,13 @@ def _like_input(result: torch.Tensor, ref: torch.Tensor, out: torch.Tensor = Non
     return result.to("cpu")
 
 
-def _elementwise_check(name, *tensors):
+def _elementwise_check(name, *tensors, dtypes=(torch.float32,)):
     t0 = tensors[0]
     for t in tensors:
-        if t.dtype != torch.float32:
-            raise TypeError(f"{name}: fp32 tensors expected, got {t.dtype}")
+        if t.dtype not in dtypes:
+            raise TypeError(f"{name}: {' or '.join(str(d) for d in dtypes)} tensors expected, got {t.dtype}")
+        if t.dtype != t0.dtype:
+            raise TypeError(f"{name}: mixed dtypes {t0.dtype} and {t.dtype}")
         if t.shape != t0.shape:
             raise ValueError(f"{name}: shape mismatch {tuple(t.shape)} vs {tuple(t0.shape)}")
         if t.device != t0.device:
@@ -73,13 +75,35 @@ def _elementwise_check(name, *tensors):
 
 
 def add(x: torch.Tensor, y: torch.Tensor, BLOCK_SIZE: int = 1024) -> torch.Tensor:
-    """out = x + y (fp32).  Mirrors add(), python/tutorials/01-vector-add.py:62-78."""
-    _elementwise_check("add", x, y)
+    """out = x + y, fp32 or bf16.  Mirrors add(), python/tutorials/01-vector-add.py:62-78 (fp32) and
+    python/tutorials/01-vector-add.loop.py:74-97 (which runs bf16 tensors)."""
+    _elementwise_check("add", x, y, dtypes=(torch.float32, torch.bfloat16))
     lib = _lib.load()
     xd, yd = _to_device(x).contiguous(), _to_device(y).contiguous()
     out = torch.empty_like(xd)
+    entry = lib.b200k_add_f32 if xd.dtype == torch.float32 else lib.b200k_add_bf16
     with _on(xd.device):
-        _lib.check(lib.b200k_add_f32(xd.data_ptr(), yd.data_ptr(), out.data_ptr(), out.numel(), BLOCK_SIZE, _stream()))
+        _lib.check(entry(xd.data_ptr(), yd.data_ptr(), out.data_ptr(), out.numel(), BLOCK_SIZE, _stream()))
+    return _like_input(out, x)
+
+
+def add_loop(x: torch.Tensor, y: torch.Tensor, n_cores: int = 130, BLOCK_SIZE: int = 1024) -> torch.Tensor:
+    """out = x + y launched like add() of python/tutorials/01-vector-add.loop.py:74-97: at most `n_cores`
+    programs, each walking row_count = cdiv(cdiv(n, BLOCK_SIZE), n_cores) consecutive blocks."""
+    from . import kernels
+    _elementwise_check("add_loop", x, y, dtypes=(torch.float32, torch.bfloat16))
+    xd, yd = _to_device(x).contiguous(), _to_device(y).contiguous()
+    out = torch.empty_like(xd)
+    n_elements = out.numel()
+    if n_elements == 0:
+        return _like_input(out, x)
+    n_rows = -(-n_elements // BLOCK_SIZE)
+    row_count = -(-n_rows // n_cores)
+    if n_rows < n_cores:
+        n_cores = n_rows
+    with _on(xd.device):
+        kernels.add_kernel_loop[lambda meta: (n_cores,)](xd, yd, out, n_elements, row_count, BLOCK_SIZE=BLOCK_SIZE,
+                                                         num_warps=1)
     return _like_input(out, x)
 
 
