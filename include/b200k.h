@@ -107,6 +107,24 @@ int b200k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K,
                      int act, int round_before_bias, void* stream);
 
 /*
+ * b200k_matmul_bf16 whose epilogue stores every output tile to n_dests destination matrices
+ * C_dests[0..n_dests) (1 <= n_dests <= 8; all [M,N] bf16 with the same leading dimension ldc, 16-byte
+ * aligned) instead of one: the single c_desc.store of the reference kernel
+ * (examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py:143) becomes n_dests TMA stores from
+ * the same staging buffer.  The destinations may be buffers of other GPUs mapped into this process
+ * (CUDA IPC or peer-mapped allocations): with C_dests[r] = peer r's full C + this GPU's row offset,
+ * every GPU holds the complete C once all ranks' launches have finished, i.e. the M-row-sharded
+ * matmul and the all-gather of C are one kernel whose NVLink traffic overlaps the main loop.
+ * C_dests is a HOST array of device pointers; it is read before the call returns.
+ * The caller orders readers of remote destinations after the launch (a stream-ordered collective or
+ * a host barrier after synchronising the stream).
+ */
+int b200k_matmul_bf16_multi(const void* A, const void* B, void* const* C_dests, int n_dests, int M, int N, int K,
+                            int64_t lda, int64_t ldb, int64_t ldc,
+                            const void* bias, int bias_kind, int64_t ldbias,
+                            int act, int round_before_bias, void* stream);
+
+/*
  * C = act(A . B) with A, B and C stored TILE-MAJOR, the memory layout the reference's pointer-based
  * matmul_kernel addresses (examples/matmul/03-matrix-multiplication.py:333-344 A, :354-362 B,
  * :378-386 C): the logical [R,S] matrix is cut into 32 x 32 tiles, tile (tr, ts) occupies the 1024

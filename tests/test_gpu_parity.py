@@ -304,6 +304,28 @@ def test_matmul_fp16_example_shapes_and_activation():
             assert float((got.view(torch.int16) != ref.view(torch.int16)).float().mean()) < 1e-2
 
 
+@pytest.mark.parametrize("shape", [(128, 128, 64), (640, 384, 200), (2304, 2304, 256)])
+def test_matmul_multi_destinations(shape):
+    # the epilogue stores every tile into all destinations (here: row blocks of three local "full C" buffers, the
+    # layout the multi-GPU all-gather uses); both kernels, tails included; neighbours of the blocks stay untouched
+    M, N, K = shape
+    a, b = gi.matmul_inputs(M, N, K, seed=31)
+    bias = gi.row_bias(N)
+    ad, bd = a.cuda(), b.cuda()
+    full = [torch.full((3 * M, N), 7.5, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    dests = [f[M:2 * M] for f in full]
+    out = ops.matmul_multi(ad, bd, dests, bias=bias.cuda(), activation="relu")
+    ref = ops.matmul_fused(ad, bd, bias.cuda(), "relu")
+    assert out.data_ptr() == dests[0].data_ptr()
+    for f in full:
+        assert torch.equal(f[M:2 * M].view(torch.int16), ref.view(torch.int16))
+        assert bool((f[:M] == 7.5).all()) and bool((f[2 * M:] == 7.5).all())
+    with pytest.raises(ValueError):
+        ops.matmul_multi(ad, bd, [])
+    with pytest.raises(ValueError):
+        ops.matmul_multi(ad, bd, [dests[0], torch.empty((M, N + 8), dtype=torch.bfloat16, device="cuda")[:, :N]])
+
+
 @pytest.mark.parametrize("case", gi.TILE32_CASES)
 def test_matmul_tile32_golden(golden_dir, case):
     # tile-major buffers in, tile-major buffer out, against what the reference's matmul_kernel source wrote

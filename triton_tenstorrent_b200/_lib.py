@@ -68,6 +68,8 @@ SIGNATURES = {
                                   c_void_p, c_int, c_int64, c_int, c_int, c_void_p]),
     "b200k_matmul_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                                  c_void_p, c_int, c_int64, c_int, c_int, c_void_p]),
+    "b200k_matmul_bf16_multi": (c_int, [c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int64,
+                                        c_int64, c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_void_p]),
     "b200k_matmul_tile32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200k_attn_fwd_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_float, c_void_p]),

@@ -436,6 +436,17 @@ int b200k_matmul_f16(const void* A, const void* B, void* C, int M, int N, int K,
   return matmul_bf16(a, static_cast<cudaStream_t>(stream), nullptr);
 }
 
+int b200k_matmul_bf16_multi(const void* A, const void* B, void* const* C_dests, int n_dests, int M, int N, int K,
+                            int64_t lda, int64_t ldb, int64_t ldc, const void* bias, int bias_kind, int64_t ldbias,
+                            int act, int round_before_bias, void* stream) {
+  clear_error();
+  if (C_dests == nullptr || n_dests < 1 || n_dests > 8)
+    return set_error(B200K_ERR_INVALID_ARG, "matmul_multi: 1..8 destinations expected (got %d)", n_dests);
+  MatmulArgs a{A, B, C_dests[0], M, N, K, lda, ldb, ldc, bias, bias_kind, ldbias, act, round_before_bias, 0, 0,
+               C_dests + 1, n_dests - 1};
+  return matmul_bf16(a, static_cast<cudaStream_t>(stream), nullptr);
+}
+
 int b200k_matmul_tile32(const void* A, const void* B, void* C, int M, int N, int K, int act, int f16, void* stream) {
   clear_error();
   if (f16 != 0 && f16 != 1) return set_error(B200K_ERR_INVALID_ARG, "matmul_tile32: f16 must be 0 or 1 (got %d)", f16);

@@ -67,6 +67,8 @@ struct MatmulArgs {
   int round_before_bias;
   int dtype;  // 0 = bf16, 1 = fp16 (A, B, C and a full [M,N] bias)
   int tile32; // 1 = A, B and C are stored tile-major (32 x 32 tiles); lda/ldb/ldc are ignored, no bias
+  void* const* extra_C;  // n_extra further [M,N] destinations with leading dimension ldc (host array of device pointers)
+  int n_extra;
 };
 // status_override: device word the kernel reports bounded-wait failures to (nullptr = the
 // per-device word from current_device_info()).

@@ -21,6 +21,7 @@
 // operand images; only tensor maps, boxes per stage and descriptor constants differ.
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "launch.h"
 #include "ptx.cuh"
@@ -56,7 +57,17 @@ struct MatmulParams {
   uint32_t idesc;                  // UMMA instruction descriptor (tile shape, operand formats and majors)
   int l2_hint;                     // CTA-pair kernel: 0 = no hints, 1 = A evict_last / B evict_first, 2 = A evict_last only
   int tile32;                      // A, B, C stored as contiguous 32 x 32 tiles (4-D tensor maps, tile coordinates)
+  int n_extra;                     // further copies of C the epilogue stores every tile to (ExtraMaps; row-major only)
   uint32_t* status;
+};
+
+// Tensor maps of additional destinations of C.  Every output tile is stored to the caller's C and to
+// each of these, straight from the epilogue's staging buffer: the destinations may be buffers of
+// other GPUs mapped into this process (peer memory), which turns the epilogue into the sending side
+// of an all-gather of C that overlaps the main loop of the following tiles.
+constexpr int MM_MAX_EXTRA = 7;
+struct alignas(64) ExtraMaps {
+  CUtensorMap m[MM_MAX_EXTRA];
 };
 
 template <int BN, int STAGES>
@@ -100,6 +111,7 @@ __device__ __forceinline__ float apply_act(float x, int act) {
 // bits; `row` is this thread's global row, `row0_warp` the warp's first row, `col0` the chunk's
 // first global column; `buf` toggles between the warp's two staging buffers.
 __device__ __forceinline__ void epilogue_chunk(const MatmulParams& p, const CUtensorMap* tmap_c,
+                                               const CUtensorMap* extra_maps,
                                                const uint32_t (&v0)[32], const uint32_t (&v1)[32], int row,
                                                int row0_warp, int col0, uint8_t* my_stage, int& buf, uint32_t lane) {
     float f[64];
@@ -200,6 +212,7 @@ __device__ __forceinline__ void epilogue_chunk(const MatmulParams& p, const CUte
           if (col0 + 32 < p.N) tma_store_tile32(tmap_c, stage_buf + 2048, (col0 >> 5) + 1, row0_warp >> 5);
         } else {
           tma_store_2d(tmap_c, stage_buf, col0, row0_warp);
+          for (int d = 0; d < p.n_extra; ++d) tma_store_2d(extra_maps + d, stage_buf, col0, row0_warp);
         }
       }
       tma_store_commit();
@@ -210,7 +223,8 @@ __device__ __forceinline__ void epilogue_chunk(const MatmulParams& p, const CUte
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(MM_THREADS, 1)
 matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                           const __grid_constant__ CUtensorMap tmap_c, const MatmulParams p) {
+                           const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ ExtraMaps extra,
+                           const MatmulParams p) {
   using L = MatmulSmem<BN, STAGES>;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
 
@@ -355,7 +369,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
           __syncwarp();
           if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
         }
-        epilogue_chunk(p, &tmap_c, v0, v1, row, m0 + q * 32, n0 + c * 64, my_stage, buf, lane);
+        epilogue_chunk(p, &tmap_c, extra.m, v0, v1, row, m0 + q * 32, n0 + c * 64, my_stage, buf, lane);
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
@@ -396,7 +410,8 @@ struct Matmul2Smem {
 template <int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MM_THREADS, 1)
 matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                                const __grid_constant__ CUtensorMap tmap_c, const MatmulParams p) {
+                                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ ExtraMaps extra,
+                                const MatmulParams p) {
   using L = Matmul2Smem<STAGES>;
   constexpr uint32_t TMEM_COLS = 512;
 
@@ -561,7 +576,7 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));
         }
-        epilogue_chunk(p, &tmap_c, v0, v1, row, m0 + q * 32, n0 + c * 64, my_stage, buf, lane);
+        epilogue_chunk(p, &tmap_c, extra.m, v0, v1, row, m0 + q * 32, n0 + c * 64, my_stage, buf, lane);
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
@@ -603,8 +618,11 @@ static void set_operand_images(MatmulParams* p, int tile32) {
   }
 }
 
-static int make_operand_tmaps(const MatmulArgs& a, CUtensorMap* ta, CUtensorMap* tb, CUtensorMap* tc) {
+static int make_operand_tmaps(const MatmulArgs& a, CUtensorMap* ta, CUtensorMap* tb, CUtensorMap* tc, ExtraMaps* extra) {
   int rc;
+  memset(extra, 0, sizeof(*extra));
+  for (int d = 0; d < a.n_extra; ++d)
+    if ((rc = make_tmap_bf16_2d(&extra->m[d], a.extra_C[d], a.N, a.M, a.ldc, 64, 32)) != 0) return rc;
   if (a.tile32) {
     if ((rc = make_tmap_tile32(ta, a.A, a.K, a.M, MM_BM)) != 0) return rc;
     if ((rc = make_tmap_tile32(tb, a.B, a.N, a.K, MM_BK)) != 0) return rc;
@@ -621,7 +639,8 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   static_assert(L::TOTAL <= 232448, "shared memory budget exceeded");
   CUtensorMap ta, tb, tc;
   int rc;
-  if ((rc = make_operand_tmaps(a, &ta, &tb, &tc)) != 0) return rc;
+  ExtraMaps extra;
+  if ((rc = make_operand_tmaps(a, &ta, &tb, &tc, &extra)) != 0) return rc;
 
   MatmulParams p;
   p.M = a.M; p.N = a.N; p.K = a.K;
@@ -640,6 +659,7 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   p.l2_hint = 0;
   p.f16 = a.dtype;
   p.tile32 = a.tile32;
+  p.n_extra = a.n_extra;
   p.idesc = umma_idesc_16bit_f32(MM_BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
   p.status = status;
 
@@ -647,7 +667,7 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   B200K_CHECK_CUDA(cudaFuncSetAttribute(matmul_bf16_tcgen05_kernel<BN, STAGES>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
-  matmul_bf16_tcgen05_kernel<BN, STAGES><<<grid, MM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p);
+  matmul_bf16_tcgen05_kernel<BN, STAGES><<<grid, MM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, extra, p);
   count_launch();
   B200K_CHECK_LAUNCH("matmul_bf16_tcgen05_kernel");
   return B200K_OK;
@@ -659,7 +679,8 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   static_assert(L::TOTAL <= 232448, "shared memory budget exceeded");
   CUtensorMap ta, tb, tc;
   int rc;
-  if ((rc = make_operand_tmaps(a, &ta, &tb, &tc)) != 0) return rc;
+  ExtraMaps extra;
+  if ((rc = make_operand_tmaps(a, &ta, &tb, &tc, &extra)) != 0) return rc;
 
   MatmulParams p;
   p.M = a.M; p.N = a.N; p.K = a.K;
@@ -677,6 +698,7 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   set_operand_images(&p, a.tile32);
   p.f16 = a.dtype;
   p.tile32 = a.tile32;
+  p.n_extra = a.n_extra;
   p.idesc = umma_idesc_16bit_f32(256, MM2_BN, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
   p.l2_hint = 2;  // keep the group's A row panel in L2 (measured +2 % at 8192^3 over no hint; B evict_first loses)
   if (const char* h = getenv("B200K_MATMUL_L2_HINT")) p.l2_hint = atoi(h);
@@ -686,7 +708,7 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   const int max_pairs = dev->sm_count / 2;
   const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
-  matmul_bf16_tcgen05_2cta_kernel<STAGES><<<2 * pairs, MM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p);
+  matmul_bf16_tcgen05_2cta_kernel<STAGES><<<2 * pairs, MM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, extra, p);
   count_launch();
   B200K_CHECK_LAUNCH("matmul_bf16_tcgen05_2cta_kernel");
   return B200K_OK;
@@ -699,6 +721,7 @@ int matmul_bf16(const MatmulArgs& a, cudaStream_t stream, uint32_t* status_overr
     if ((a.M & 31) || (a.N & 31) || (a.K & 31))
       return set_error(B200K_ERR_INVALID_ARG, "matmul: tile-major operands need M, N, K multiples of 32 (got %d, %d, %d)", a.M, a.N, a.K);
     if (a.bias_kind != B200K_BIAS_NONE) return set_error(B200K_ERR_INVALID_ARG, "matmul: tile-major operands take no bias");
+    if (a.n_extra != 0) return set_error(B200K_ERR_INVALID_ARG, "matmul: tile-major operands take no extra destinations");
   } else {
     if (a.lda < a.K || a.ldb < a.N || a.ldc < a.N) return set_error(B200K_ERR_INVALID_ARG, "matmul: leading dimension smaller than the row length");
     if ((a.lda & 7) || (a.ldb & 7) || (a.ldc & 7))
@@ -707,6 +730,11 @@ int matmul_bf16(const MatmulArgs& a, cudaStream_t stream, uint32_t* status_overr
   }
   if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) | reinterpret_cast<uintptr_t>(a.C)) & 15u)
     return set_error(B200K_ERR_INVALID_ARG, "matmul: A, B and C must be 16-byte aligned");
+  if (a.n_extra < 0 || a.n_extra > MM_MAX_EXTRA || (a.n_extra > 0 && a.extra_C == nullptr))
+    return set_error(B200K_ERR_INVALID_ARG, "matmul: 0..%d extra destinations supported (got %d)", MM_MAX_EXTRA, a.n_extra);
+  for (int d = 0; d < a.n_extra; ++d)
+    if (a.extra_C[d] == nullptr || (reinterpret_cast<uintptr_t>(a.extra_C[d]) & 15u))
+      return set_error(B200K_ERR_INVALID_ARG, "matmul: extra destination %d is null or not 16-byte aligned", d);
   if (a.bias_kind < B200K_BIAS_NONE || a.bias_kind > B200K_BIAS_FULL_BF16) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad bias_kind %d", a.bias_kind);
   if (a.dtype != 0 && a.dtype != 1) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad element type %d", a.dtype);
   if (a.act < B200K_ACT_NONE || a.act > B200K_ACT_LEAKY_RELU) return set_error(B200K_ERR_INVALID_ARG, "matmul: bad act %d", a.act);

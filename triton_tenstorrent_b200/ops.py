@@ -9,12 +9,13 @@ result is copied back, which is what the reference's D2M launcher does on every 
 from __future__ import annotations
 
 import contextlib
+import ctypes
 
 import torch
 
 from . import _lib
 
-__all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_fused", "matmul_tma_fused", "attention",
+__all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_multi", "matmul_fused", "matmul_tma_fused", "attention",
            "attention_with_lse", "device_status"]
 
 
@@ -239,6 +240,45 @@ def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT
         _lib.check(entry(ad.data_ptr(), bd.data_ptr(), c.data_ptr(), M, N, K, ad.stride(0), bd.stride(0),
                          c.stride(0), bias_ptr, bias_kind, ldbias, act, round_before_bias, _stream()))
     return c
+
+
+def matmul_multi(a: torch.Tensor, b: torch.Tensor, dests, bias: torch.Tensor = None, activation: str = ""):
+    """C = act(A.B [+ bias[N]]) stored by the kernel's epilogue into every tensor of `dests` (1..8 bf16 [M,N]
+    tensors with one common row stride).  The tensors may live on other GPUs of the box as long as their memory is
+    mapped into this process (sharding.GatheredRows does that): the matmul then doubles as the sending side of an
+    all-gather of C.  Readers of remote destinations must be ordered after the launch by the caller."""
+    if activation not in _ACTIVATIONS:
+        raise ValueError(f"unknown activation {activation!r}")
+    dests = list(dests)
+    if not 1 <= len(dests) <= 8:
+        raise ValueError(f"matmul_multi: 1..8 destinations expected, got {len(dests)}")
+    assert a.shape[1] == b.shape[0], "Incompatible dimensions"
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("matmul_multi: bf16 operands expected")
+    if not (a.is_cuda and b.is_cuda):
+        raise ValueError("matmul_multi: operands must live on the GPU")
+    lib = _lib.load()
+    ad, bd = _row_major_2d(a, "a"), _row_major_2d(b, "b")
+    M, K = ad.shape
+    _, N = bd.shape
+    ldc = dests[0].stride(0)
+    for i, d in enumerate(dests):
+        if (not d.is_cuda or d.dtype != torch.bfloat16 or tuple(d.shape) != (M, N) or d.stride(1) != 1
+                or d.stride(0) != ldc or ldc % 8 != 0 or d.data_ptr() % 16 != 0):
+            raise ValueError(f"matmul_multi: destination {i} must be a bf16 [{M},{N}] CUDA tensor with unit inner stride, "
+                             f"row stride {ldc} (a multiple of 8) and a 16-byte aligned base")
+    bias_ptr, bias_kind = 0, _lib.BIAS_NONE
+    if bias is not None:
+        bias = bias.contiguous()
+        if bias.dtype != torch.float32 or tuple(bias.shape) != (N,) or bias.device != ad.device:
+            raise ValueError(f"bias must be fp32 [N={N}] on {ad.device}")
+        bias_ptr, bias_kind = bias.data_ptr(), _lib.BIAS_ROW_F32
+    ptrs = (ctypes.c_void_p * len(dests))(*[d.data_ptr() for d in dests])
+    with _on(ad.device):
+        _lib.check(lib.b200k_matmul_bf16_multi(ad.data_ptr(), bd.data_ptr(), ptrs, len(dests), M, N, K, ad.stride(0),
+                                               bd.stride(0), ldc, bias_ptr, bias_kind, 0, _ACTIVATIONS[activation], 0,
+                                               _stream()))
+    return dests[0]
 
 
 def matmul_tma(a: torch.Tensor, b: torch.Tensor, warp_specialize: bool = True, out: torch.Tensor = None) -> torch.Tensor:
