@@ -210,6 +210,25 @@ typedef struct b200k_props {
 int b200k_device_props(int device, b200k_props* out);
 
 /*
+ * Sharing a device buffer between the per-GPU processes of one box, for b200k_matmul_bf16_multi's remote
+ * destinations.  b200k_ipc_export describes the allocation that contains `ptr` (a CUDA IPC handle of the
+ * allocation, the offset of `ptr` inside it, the device); the 88 bytes can be sent to another process by any
+ * means.  b200k_ipc_open maps that allocation into the CALLING device's context with peer access enabled and
+ * returns the address corresponding to `ptr`; repeated opens of one allocation reuse the mapping, which stays
+ * until the process exits (the exporter must keep the allocation alive as long as importers use it).  Fails
+ * with B200K_ERR_UNSUPPORTED when the current device cannot access the exporting device directly.
+ */
+typedef struct b200k_ipc_handle {
+  unsigned char handle[64];
+  int64_t offset;
+  int64_t size;   /* bytes of the allocation */
+  int32_t device; /* exporting device ordinal */
+  int32_t _pad;
+} b200k_ipc_handle;
+int b200k_ipc_export(const void* ptr, b200k_ipc_handle* out);
+int b200k_ipc_open(const b200k_ipc_handle* h, void** ptr);
+
+/*
  * Contiguous block range of worker `w` out of `workers` over `num_blocks` blocks:
  * base = nb / W, rem = nb % W, worker w gets [w*base + min(w,rem), +base + (w<rem)).
  * Replaces: the per-core partition of npu/lib/TritonNPUToTenstorrent/D2M/SPMDOpToD2M.cpp:53-113.

@@ -24,6 +24,7 @@ def main():
         bias = (torch.randn(N, generator=gb) * 0.1).cuda() if with_bias else None
         act = "relu" if with_bias else ""
         gathered = sharding.GatheredRows(rows, N)
+        print(f"rank {rank}: {len(gathered.remote_blocks())} remote copies mapped", flush=True)
         gathered.local.fill_(7.5)                      # sentinel: every row block must be overwritten
         torch.cuda.synchronize()
         dist.barrier()                                 # nobody stores into a copy that is still being filled

@@ -314,7 +314,7 @@ def test_matmul_multi_destinations(shape):
     ad, bd = a.cuda(), b.cuda()
     full = [torch.full((3 * M, N), 7.5, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
     dests = [f[M:2 * M] for f in full]
-    out = ops.matmul_multi(ad, bd, dests, bias=bias.cuda(), activation="relu")
+    out = ops.matmul_multi(ad, bd, dests[:2], bias=bias.cuda(), activation="relu", remote_ptrs=[dests[2].data_ptr()])
     ref = ops.matmul_fused(ad, bd, bias.cuda(), "relu")
     assert out.data_ptr() == dests[0].data_ptr()
     for f in full:

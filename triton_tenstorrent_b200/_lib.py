@@ -42,6 +42,12 @@ class Arg(Structure):
     _fields_ = [("kind", c_int32), ("_pad", c_int32), ("v", _ArgValue)]
 
 
+class IpcHandle(Structure):
+    """b200k_ipc_handle: 88 bytes that describe an exported device allocation."""
+    _fields_ = [("handle", ctypes.c_ubyte * 64), ("offset", c_int64), ("size", c_int64), ("device", c_int32),
+                ("_pad", c_int32)]
+
+
 class Props(Structure):
     """b200k_props."""
     _fields_ = [
@@ -78,6 +84,8 @@ SIGNATURES = {
     "b200k_attn_supported": (c_int, [c_int, c_int]),
     "b200k_launch": (c_int, [c_char_p, c_int, c_int, c_int, c_void_p, POINTER(Arg), c_int]),
     "b200k_device_props": (c_int, [c_int, POINTER(Props)]),
+    "b200k_ipc_export": (c_int, [c_void_p, POINTER(IpcHandle)]),
+    "b200k_ipc_open": (c_int, [POINTER(IpcHandle), POINTER(c_void_p)]),
     "b200k_block_range": (c_int, [c_int64, c_int, c_int, POINTER(c_int64), POINTER(c_int64)]),
     "b200k_device_status": (c_int, [c_void_p, POINTER(c_uint32)]),
     "b200k_selftest_wait_timeout": (c_int, [c_int64, c_void_p]),

@@ -8,6 +8,7 @@
 #include <mutex>
 #include <string>
 #include <unordered_map>
+#include <vector>
 
 #include "launch.h"
 
@@ -484,6 +485,74 @@ int b200k_device_props(int device, b200k_props* out) {
   out->cc_minor = prop.minor;
   out->total_mem = static_cast<int64_t>(prop.totalGlobalMem);
   strncpy(out->name, prop.name, sizeof(out->name) - 1);
+  return B200K_OK;
+}
+
+// ---- CUDA IPC: one mapping per imported allocation, kept for the life of the process
+namespace {
+struct IpcMapping {
+  unsigned char handle[64];
+  int importer_device;
+  void* base;
+};
+std::vector<IpcMapping> g_ipc_mappings;
+std::mutex g_ipc_mutex;
+typedef CUresult (*GetAddressRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+}  // namespace
+
+int b200k_ipc_export(const void* ptr, b200k_ipc_handle* out) {
+  clear_error();
+  if (ptr == nullptr || out == nullptr) return set_error(B200K_ERR_INVALID_ARG, "ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle size");
+  cudaPointerAttributes attr;
+  B200K_CHECK_CUDA(cudaPointerGetAttributes(&attr, ptr));
+  if (attr.type != cudaMemoryTypeDevice) return set_error(B200K_ERR_INVALID_ARG, "ipc_export: not a device pointer");
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPointByVersion("cuMemGetAddressRange", &fn, 12000, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess || fn == nullptr)
+    return set_error(B200K_ERR_CUDA, "ipc_export: cuMemGetAddressRange is not available from this driver");
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUresult r = reinterpret_cast<GetAddressRangeFn>(fn)(&base, &size, reinterpret_cast<CUdeviceptr>(ptr));
+  if (r != CUDA_SUCCESS) return set_error(B200K_ERR_CUDA, "ipc_export: cuMemGetAddressRange failed with CUresult %d", (int)r);
+  memset(out, 0, sizeof(*out));
+  cudaIpcMemHandle_t h;
+  B200K_CHECK_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  memcpy(out->handle, &h, 64);
+  out->offset = static_cast<int64_t>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  out->size = static_cast<int64_t>(size);
+  out->device = attr.device;
+  return B200K_OK;
+}
+
+int b200k_ipc_open(const b200k_ipc_handle* h, void** ptr) {
+  clear_error();
+  if (h == nullptr || ptr == nullptr) return set_error(B200K_ERR_INVALID_ARG, "ipc_open: null argument");
+  if (h->offset < 0 || h->offset >= h->size) return set_error(B200K_ERR_INVALID_ARG, "ipc_open: offset outside the allocation");
+  int dev = -1;
+  B200K_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev != h->device) {
+    int can = 0;
+    B200K_CHECK_CUDA(cudaDeviceCanAccessPeer(&can, dev, h->device));
+    if (!can) return set_error(B200K_ERR_UNSUPPORTED, "ipc_open: device %d cannot access device %d directly", dev, h->device);
+  }
+  std::lock_guard<std::mutex> lock(g_ipc_mutex);
+  for (const IpcMapping& m : g_ipc_mappings)
+    if (m.importer_device == dev && memcmp(m.handle, h->handle, 64) == 0) {
+      *ptr = static_cast<char*>(m.base) + h->offset;
+      return B200K_OK;
+    }
+  cudaIpcMemHandle_t ch;
+  memcpy(&ch, h->handle, 64);
+  void* base = nullptr;
+  B200K_CHECK_CUDA(cudaIpcOpenMemHandle(&base, ch, cudaIpcMemLazyEnablePeerAccess));
+  IpcMapping m;
+  memcpy(m.handle, h->handle, 64);
+  m.importer_device = dev;
+  m.base = base;
+  g_ipc_mappings.push_back(m);
+  *ptr = static_cast<char*>(base) + h->offset;
   return B200K_OK;
 }
 

@@ -242,16 +242,18 @@ def _matmul_call(a, b, c=None, bias=None, bias_kind=_lib.BIAS_NONE, act=_lib.ACT
     return c
 
 
-def matmul_multi(a: torch.Tensor, b: torch.Tensor, dests, bias: torch.Tensor = None, activation: str = ""):
-    """C = act(A.B [+ bias[N]]) stored by the kernel's epilogue into every tensor of `dests` (1..8 bf16 [M,N]
-    tensors with one common row stride).  The tensors may live on other GPUs of the box as long as their memory is
-    mapped into this process (sharding.GatheredRows does that): the matmul then doubles as the sending side of an
-    all-gather of C.  Readers of remote destinations must be ordered after the launch by the caller."""
+def matmul_multi(a: torch.Tensor, b: torch.Tensor, dests, bias: torch.Tensor = None, activation: str = "",
+                 remote_ptrs=()):
+    """C = act(A.B [+ bias[N]]) stored by the kernel's epilogue into every tensor of `dests` (bf16 [M,N] tensors with
+    one common row stride) and to every address of `remote_ptrs` (device addresses of [M,N] blocks with that same row
+    stride, e.g. row blocks of other GPUs' buffers mapped by sharding.GatheredRows); at most 8 destinations in
+    all.  With remote destinations the matmul doubles as the sending side of an all-gather of C.  Readers of
+    remote destinations must be ordered after the launch by the caller.  Returns dests[0]."""
     if activation not in _ACTIVATIONS:
         raise ValueError(f"unknown activation {activation!r}")
-    dests = list(dests)
-    if not 1 <= len(dests) <= 8:
-        raise ValueError(f"matmul_multi: 1..8 destinations expected, got {len(dests)}")
+    dests, remote_ptrs = list(dests), [int(p) for p in remote_ptrs]
+    if len(dests) < 1 or len(dests) + len(remote_ptrs) > 8:
+        raise ValueError(f"matmul_multi: 1..8 destinations expected, got {len(dests)} + {len(remote_ptrs)}")
     assert a.shape[1] == b.shape[0], "Incompatible dimensions"
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise TypeError("matmul_multi: bf16 operands expected")
@@ -263,19 +265,23 @@ def matmul_multi(a: torch.Tensor, b: torch.Tensor, dests, bias: torch.Tensor = N
     _, N = bd.shape
     ldc = dests[0].stride(0)
     for i, d in enumerate(dests):
-        if (not d.is_cuda or d.dtype != torch.bfloat16 or tuple(d.shape) != (M, N) or d.stride(1) != 1
-                or d.stride(0) != ldc or ldc % 8 != 0 or d.data_ptr() % 16 != 0):
-            raise ValueError(f"matmul_multi: destination {i} must be a bf16 [{M},{N}] CUDA tensor with unit inner stride, "
-                             f"row stride {ldc} (a multiple of 8) and a 16-byte aligned base")
+        if (not d.is_cuda or d.device != ad.device or d.dtype != torch.bfloat16 or tuple(d.shape) != (M, N)
+                or d.stride(1) != 1 or d.stride(0) != ldc or ldc % 8 != 0 or d.data_ptr() % 16 != 0):
+            raise ValueError(f"matmul_multi: destination {i} must be a bf16 [{M},{N}] tensor on {ad.device} with unit "
+                             f"inner stride, row stride {ldc} (a multiple of 8) and a 16-byte aligned base")
+    for p in remote_ptrs:
+        if p == 0 or p % 16 != 0:
+            raise ValueError("matmul_multi: remote destinations must be non-null and 16-byte aligned")
     bias_ptr, bias_kind = 0, _lib.BIAS_NONE
     if bias is not None:
         bias = bias.contiguous()
         if bias.dtype != torch.float32 or tuple(bias.shape) != (N,) or bias.device != ad.device:
             raise ValueError(f"bias must be fp32 [N={N}] on {ad.device}")
         bias_ptr, bias_kind = bias.data_ptr(), _lib.BIAS_ROW_F32
-    ptrs = (ctypes.c_void_p * len(dests))(*[d.data_ptr() for d in dests])
+    all_ptrs = [d.data_ptr() for d in dests] + remote_ptrs
+    ptrs = (ctypes.c_void_p * len(all_ptrs))(*all_ptrs)
     with _on(ad.device):
-        _lib.check(lib.b200k_matmul_bf16_multi(ad.data_ptr(), bd.data_ptr(), ptrs, len(dests), M, N, K, ad.stride(0),
+        _lib.check(lib.b200k_matmul_bf16_multi(ad.data_ptr(), bd.data_ptr(), ptrs, len(all_ptrs), M, N, K, ad.stride(0),
                                                bd.stride(0), ldc, bias_ptr, bias_kind, 0, _ACTIVATIONS[activation], 0,
                                                _stream()))
     return dests[0]

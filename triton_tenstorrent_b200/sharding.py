@@ -53,10 +53,12 @@ class GatheredRows:
     """A full [world * rows, N] bf16 matrix on every rank whose copies are all mapped into every rank's process,
     so that one rank's matmul epilogue can store its row block into all of them (ops.matmul_multi).
 
-    Each rank allocates its copy with torch, exports it as a CUDA IPC handle
-    (torch.multiprocessing.reductions.reduce_tensor) and opens the other ranks' handles; the handles travel
-    through all_gather_object of the process group.  Needs one process per GPU on one box with peer access
-    (NVLink / NVSwitch).  `dests()` lists, own copy first, the views of this rank's row block in every copy.
+    Each rank allocates its copy with torch, exports the allocation as a CUDA IPC handle (b200k_ipc_export) and maps
+    the other ranks' allocations into its own device's context with peer access (b200k_ipc_open); the 88-byte
+    handles travel through all_gather_object of the process group.  Needs one process per GPU on one box with
+    direct peer access (NVLink / NVSwitch).  The mappings stay until the process exits, so keep `local` alive and
+    do not empty torch's allocator cache while other ranks still store into it.
+    `remote_blocks()` lists the addresses of this rank's row block inside every other rank's copy.
     `fence()` is the stream-ordered point after which every rank's block has arrived in the local copy: a
     one-element all-reduce on the current stream (it follows this rank's stores in stream order, and completes
     only when every rank has reached it)."""
@@ -64,7 +66,6 @@ class GatheredRows:
     def __init__(self, rows: int, N: int, group=None, device=None):
         import torch
         import torch.distributed as dist
-        from torch.multiprocessing.reductions import reduce_tensor
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -72,21 +73,30 @@ class GatheredRows:
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.local = torch.empty((self.world * rows, N), dtype=torch.bfloat16, device=device)
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
-        handles = [None] * self.world
-        dist.all_gather_object(handles, reduce_tensor(self.local), group=group)
-        with torch.cuda.device(device):   # peer access is enabled for the device current while a handle is opened
-            self.copies = [self.local if r == self.rank else fn(*args) for r, (fn, args) in enumerate(handles)]
-        for r, c in enumerate(self.copies):
-            if tuple(c.shape) != tuple(self.local.shape) or c.dtype != self.local.dtype:
-                raise RuntimeError(f"rank {r} exported a {tuple(c.shape)} {c.dtype} buffer")
+        lib = _lib.load()
+        mine = _lib.IpcHandle()
+        with torch.cuda.device(device):
+            _lib.check(lib.b200k_ipc_export(self.local.data_ptr(), ctypes.byref(mine)))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(mine), group=group)
+            self.copy_ptrs = []
+            for r, raw in enumerate(handles):
+                if r == self.rank:
+                    self.copy_ptrs.append(self.local.data_ptr())
+                    continue
+                h = _lib.IpcHandle.from_buffer_copy(raw)
+                p = ctypes.c_void_p()
+                _lib.check(lib.b200k_ipc_open(ctypes.byref(h), ctypes.byref(p)))
+                self.copy_ptrs.append(p.value)
 
-    def block(self, copy_rank: int, block_rank: int):
-        """Rows of `block_rank` inside rank `copy_rank`'s copy."""
-        return self.copies[copy_rank][block_rank * self.rows:(block_rank + 1) * self.rows]
+    def own_block(self):
+        """This rank's rows inside its own copy (a tensor view)."""
+        return self.local[self.rank * self.rows:(self.rank + 1) * self.rows]
 
-    def dests(self):
-        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
-        return [self.block(r, self.rank) for r in order]
+    def remote_blocks(self):
+        """Addresses of this rank's rows inside the other ranks' copies."""
+        off = self.rank * self.rows * self.N * 2
+        return [p + off for r, p in enumerate(self.copy_ptrs) if r != self.rank]
 
     def fence(self):
         import torch.distributed as dist
@@ -97,6 +107,7 @@ def matmul_all_gather(a_shard, b, gathered: "GatheredRows", bias=None, activatio
     """This rank's rows of C = act(A.B [+ bias]) computed once and stored by the kernel into every rank's copy of
     the full C; returns the local full C, complete after the fence."""
     from . import ops
-    ops.matmul_multi(a_shard, b, gathered.dests(), bias=bias, activation=activation)
+    ops.matmul_multi(a_shard, b, [gathered.own_block()], bias=bias, activation=activation,
+                     remote_ptrs=gathered.remote_blocks())
     gathered.fence()
     return gathered.local
