@@ -427,8 +427,40 @@ def secondary_workloads(torch, ops, gi, peaks, dist, world, rank, a, b, c, shard
         ash, csh = a[r0:r1], c[r0:r1]
         ms = time_region(lambda: ops.matmul_tma(ash, b, True, out=csh), 20, dist, torch)
         out["strong_8192_shard"] = {"rows_per_gpu": r1 - r0, "ms": ms, "TFLOP/s_total": FLOP_PER_STEP / ms / 1e9}
-        ms = time_region(lambda: sharding.all_gather_rows(csh), 10, dist, torch)
-        out["all_gather_C_nccl"] = {"ms": ms, "bytes_out": M * N * 2, "GB/s_bus": (world - 1) / world * M * N * 2 / ms / 1e6}
+        ms_ag = time_region(lambda: sharding.all_gather_rows(csh), 10, dist, torch)
+        out["all_gather_C_nccl"] = {"ms": ms_ag, "bytes_out": M * N * 2, "GB/s_bus": (world - 1) / world * M * N * 2 / ms_ag / 1e6}
+        # the same result from ONE kernel per rank: the matmul epilogue stores its rows into every rank's copy of C
+        # over NVLink (peer-mapped buffers), followed by a one-element all-reduce as the fence
+        if (r1 - r0) * world == M:
+            gathered = sharding.GatheredRows(r1 - r0, N)
+            torch.cuda.synchronize()
+            dist.barrier()
+            sep = lambda: sharding.all_gather_rows(ops.matmul_tma(ash, b, True, out=csh))
+            fused = lambda: sharding.matmul_all_gather(ash, b, gathered)
+            sep(); fused()
+            ms_sep = time_region(sep, 20, dist, torch)
+            ms_fused = time_region(fused, 20, dist, torch)
+            sent = (world - 1) * (r1 - r0) * N * 2
+            out["strong_8192_matmul_plus_all_gather"] = {
+                "ms_matmul_then_nccl_all_gather": ms_sep, "ms_fused_epilogue_stores": ms_fused,
+                "speedup": ms_sep / ms_fused, "nvlink_bytes_sent_per_gpu": sent,
+                "GB/s_sent_per_gpu_fused": sent / ms_fused / 1e6}
+            # weak-scaling form: every rank's full 8192-row block gathered into a [world*8192, 8192] matrix
+            big = sharding.GatheredRows(M, N)
+            torch.cuda.synchronize()
+            dist.barrier()
+            sep = lambda: sharding.all_gather_rows(ops.matmul_tma(a, b, True, out=c))
+            fused = lambda: sharding.matmul_all_gather(a, b, big)
+            sep(); fused()
+            ms_sep = time_region(sep, 5, dist, torch)
+            ms_fused = time_region(fused, 5, dist, torch)
+            sent = (world - 1) * M * N * 2
+            out["weak_8192_per_gpu_matmul_plus_all_gather"] = {
+                "ms_matmul_then_nccl_all_gather": ms_sep, "ms_fused_epilogue_stores": ms_fused,
+                "speedup": ms_sep / ms_fused, "nvlink_bytes_sent_per_gpu": sent,
+                "GB/s_sent_per_gpu_fused": sent / ms_fused / 1e6,
+                "TFLOP/s_total_fused": world * FLOP_PER_STEP / ms_fused / 1e9}
+            del big, gathered
     return out
 
 
