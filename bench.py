@@ -361,6 +361,15 @@ def secondary_workloads(torch, ops, gi, peaks, dist, world, rank, a, b, c, shard
     xd, yd = x.cuda(), y.cuda()
     ms = quick_ms(lambda: ops.add(xd, yd), torch, rep=50)
     out["add_n98432"] = {"ms": ms, "GB/s": 12 * 98432 / ms / 1e6, "note": "L2-resident, launch-latency bound"}
+    # the same call recorded in a CUDA graph (20 launches per replay): what is left is the kernel itself
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(20):
+            held = ops.add(xd, yd)
+    ms = quick_ms(graph.replay, torch, rep=20) / 20
+    out["add_n98432_cuda_graph"] = {"ms": ms, "GB/s": 12 * 98432 / ms / 1e6, "note": "20 launches per graph replay"}
+    del graph, held
     n = 1 << 26
     xb, yb = torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
     # 805 MB / 537 MB per launch: larger than L2, so back-to-back launches are a valid bandwidth measurement;

@@ -168,6 +168,16 @@ int b200k_attn_fwd_bf16(const void* q, const void* k, const void* v, void* o, fl
  */
 int b200k_attn_fwd_bf16_noalloc(const void* q, const void* k, const void* v, void* o,
                                 int Z, int H, int N_CTX, int D, int causal, float sm_scale, void* stream);
+/*
+ * b200k_attn_fwd_bf16 whose epilogue stores every O tile to n_dests destinations o_dests[0..n_dests)
+ * (1 <= n_dests <= 8, each a contiguous [Z,H,N_CTX,D] bf16 block, 16-byte aligned) instead of one; the
+ * row statistics go to lse2 only.  As with b200k_matmul_bf16_multi the further destinations may be buffers
+ * of other GPUs mapped into this process, so a (batch, head)-sharded attention leaves the complete O on
+ * every GPU without a separate all-gather.  o_dests is a HOST array of device pointers.
+ */
+int b200k_attn_fwd_bf16_multi(const void* q, const void* k, const void* v, void* const* o_dests, int n_dests,
+                              float* lse2, int Z, int H, int N_CTX, int D, int causal, float sm_scale, void* stream);
+
 /* 1 if b200k_attn_fwd_bf16 has a kernel for this (D, N_CTX), else 0. */
 int b200k_attn_supported(int D, int N_CTX);
 

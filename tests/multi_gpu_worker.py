@@ -41,6 +41,23 @@ def main():
         ok = ok and same
         dist.barrier()
         del gathered
+    # attention sharded by (batch, head): every rank's heads, O gathered by the kernel's epilogue
+    for (Hs, S, D, causal) in ((2, 256, 128, True), (3, 512, 64, False)):
+        g = torch.Generator(device="cpu").manual_seed(200 + rank)
+        q, k, v = (torch.randn(1, Hs, S, D, generator=g).bfloat16().cuda() for _ in range(3))
+        gathered = sharding.GatheredRows(Hs * S, D)
+        gathered.local.fill_(7.5)
+        torch.cuda.synchronize()
+        dist.barrier()
+        full = sharding.attention_all_gather(q, k, v, causal, D ** -0.5, gathered)
+        torch.cuda.synchronize()
+        ref = sharding.all_gather_rows(ops.attention(q, k, v, causal, D ** -0.5).reshape(Hs * S, D))
+        torch.cuda.synchronize()
+        same = torch.equal(full.view(torch.int16), ref.view(torch.int16))
+        print(f"rank {rank}: attention heads={Hs} S={S} D={D} causal={causal} bit-equal={same}", flush=True)
+        ok = ok and same
+        dist.barrier()
+        del gathered
     status = ops.device_status()
     ok = ok and status == 0
     flag = torch.tensor([1 if ok else 0], device="cuda")

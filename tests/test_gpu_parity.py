@@ -388,6 +388,57 @@ def test_matmul_rejects_bad_arguments():
     assert rc == _lib.ERR_INVALID_ARG and "16-byte aligned" in _lib.last_error()
 
 
+@pytest.mark.parametrize("D,causal", [(128, True), (64, False)])
+def test_attention_multi_destinations(D, causal):
+    Z, H, S = 1, 3, 384
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=51)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    rows = Z * H * S
+    full = [torch.full((3 * rows, D), 7.5, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    out, m = ops.attention_multi(qd, kd, vd, causal, D ** -0.5, full[0][rows:2 * rows],
+                                 remote_ptrs=[f[rows:2 * rows].data_ptr() for f in full[1:]])
+    ref_o, ref_m = ops.attention_with_lse(qd, kd, vd, causal, D ** -0.5)
+    assert torch.equal(m, ref_m)
+    for f in full:
+        assert torch.equal(f[rows:2 * rows].view(torch.int16), ref_o.reshape(rows, D).view(torch.int16))
+        assert bool((f[:rows] == 7.5).all()) and bool((f[2 * rows:] == 7.5).all())
+
+
+def test_cuda_graph_capture_and_replay():
+    # the launch-bound calls (the reference's own add at n = 98432 is one) can be recorded once and replayed: every
+    # entry point launches on the caller's stream and neither allocates nor synchronises once the device is warm
+    n = 98432
+    x, y = gi.add_inputs(n)
+    a, b = gi.matmul_inputs(256, 512, 192, seed=41)
+    q, k, v = gi.attn_inputs(1, 2, 256, 128, seed=41)
+    sx, sy, sa, sb = x.cuda(), y.cuda(), a.cuda(), b.cuda()
+    sq, sk, sv = q.cuda(), k.cuda(), v.cuda()
+    eager = lambda: (ops.add(sx, sy), ops.sin(sx), ops.matmul(sa, sb, "leaky_relu"), ops.attention(sq, sk, sv, True, 0.1))
+    want1 = [t.clone() for t in eager()]                       # also warms every kernel up
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = eager()
+    graph.replay()
+    torch.cuda.synchronize()
+    for got, want in zip(outs, want1):
+        assert _bits_equal(got.float(), want.float())
+    # new contents in the captured input buffers, replay again
+    x2, y2 = gi.add_inputs(n, seed=8)
+    a2, b2 = gi.matmul_inputs(256, 512, 192, seed=42)
+    q2, k2, v2 = gi.attn_inputs(1, 2, 256, 128, seed=42)
+    for dst, src in ((sx, x2), (sy, y2), (sa, a2), (sb, b2), (sq, q2), (sk, k2), (sv, v2)):
+        dst.copy_(src)
+    graph.replay()
+    torch.cuda.synchronize()
+    got2 = [t.clone() for t in outs]
+    want2 = eager()
+    torch.cuda.synchronize()
+    for got, want in zip(got2, want2):
+        assert _bits_equal(got.float(), want.float())
+    assert _bits_equal(got2[0], oracle.add(x2, y2).cuda())
+
+
 # ------------------------------------------------------------------------------------------------ attention
 @pytest.mark.parametrize("case", gi.ATTN_CASES)
 def test_attention_golden(golden_dir, case):

@@ -22,6 +22,7 @@
 // rounding, and M = m + log2(l) is unchanged.
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <atomic>
 #include <mutex>
@@ -60,6 +61,7 @@ struct AttnParams {
   float qk_scale;  // sm_scale * 1.44269504 (fp32 product, as the reference computes it)
   float* lse2;
   uint32_t* status;
+  int n_extra;     // further copies of O the epilogue stores every tile to (ExtraMaps)
 };
 
 struct AttnItem {
@@ -121,7 +123,7 @@ template <int D>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
-                             const AttnParams p) {
+                             const __grid_constant__ ExtraMaps extra, const AttnParams p) {
   constexpr uint32_t IDESC_S = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);   // Q (K-major) x K^T (K-major)
   constexpr uint32_t IDESC_PV = umma_idesc_bf16_f32(AT_BM, D, 0, 1);      // P (TMEM) x V (N-major)
   using Cfg = AttnCfg<D>;
@@ -466,6 +468,11 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         const int y = static_cast<int>(out_row) + q * 32;
 #pragma unroll
         for (int bx = 0; bx < Cfg::NBOX; ++bx) tma_store_2d(&tmap_o, stage + bx * AT_BOX_BYTES + q * 32 * 128, bx * 64, y);
+        for (int d = 0; d < p.n_extra; ++d) {
+#pragma unroll
+          for (int bx = 0; bx < Cfg::NBOX; ++bx)
+            tma_store_2d(&extra.m[d], stage + bx * AT_BOX_BYTES + q * 32 * 128, bx * 64, y);
+        }
         tma_store_commit();
         tma_store_wait_read<0>();
         mbar_arrive(&q_empty[t]);  // the Q buffer may be refilled
@@ -508,6 +515,11 @@ static int attn_check_args(const AttnArgs& a) {
   if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
        reinterpret_cast<uintptr_t>(a.o)) & 15u)
     return set_error(B200K_ERR_INVALID_ARG, "attention: q, k, v, o must be 16-byte aligned");
+  if (a.n_extra < 0 || a.n_extra > MAX_EXTRA_DESTS || (a.n_extra > 0 && a.extra_o == nullptr))
+    return set_error(B200K_ERR_INVALID_ARG, "attention: 0..%d extra destinations supported (got %d)", MAX_EXTRA_DESTS, a.n_extra);
+  for (int d = 0; d < a.n_extra; ++d)
+    if (a.extra_o[d] == nullptr || (reinterpret_cast<uintptr_t>(a.extra_o[d]) & 15u))
+      return set_error(B200K_ERR_INVALID_ARG, "attention: extra destination %d is null or not 16-byte aligned", d);
   const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
   if (rows > 0x7FFFFFFF) return set_error(B200K_ERR_INVALID_ARG, "attention: Z*H*N_CTX exceeds 2^31-1 rows");
   if (!(a.sm_scale > 0.f) || !isfinite(a.sm_scale)) return set_error(B200K_ERR_INVALID_ARG, "attention: sm_scale must be positive and finite");
@@ -524,6 +536,10 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
   if ((rc = make_tmap_bf16_2d(&tk, a.k, D, rows, D, 64, AT_BN)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tv, a.v, D, rows, D, 64, AT_BN)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&to, a.o, D, rows, D, 64, 32)) != 0) return rc;
+  ExtraMaps extra;
+  memset(&extra, 0, sizeof(extra));
+  for (int d = 0; d < a.n_extra; ++d)
+    if ((rc = make_tmap_bf16_2d(&extra.m[d], a.extra_o[d], D, rows, D, 64, 32)) != 0) return rc;
 
   AttnParams p;
   p.ZH = a.Z * a.H;
@@ -535,6 +551,7 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
   p.qk_scale = a.sm_scale * 1.44269504f;
   p.lse2 = a.lse2;
   p.status = status;
+  p.n_extra = a.n_extra;
 
   int grid = pick_grid(sm_count, p.num_items, p.num_pairs, p.causal != 0);
   if (const char* g = getenv("B200K_ATTN_GRID")) { int v = atoi(g); if (v > 0 && v <= p.num_items) grid = v; }
@@ -542,11 +559,11 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
   if (a.D == 64) {
     B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           AttnCfg<64>::SMEM_TOTAL));
-    attn_fwd_bf16_tcgen05_kernel<64><<<grid, AT_THREADS, AttnCfg<64>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, p);
+    attn_fwd_bf16_tcgen05_kernel<64><<<grid, AT_THREADS, AttnCfg<64>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, extra, p);
   } else {
     B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           AttnCfg<128>::SMEM_TOTAL));
-    attn_fwd_bf16_tcgen05_kernel<128><<<grid, AT_THREADS, AttnCfg<128>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, p);
+    attn_fwd_bf16_tcgen05_kernel<128><<<grid, AT_THREADS, AttnCfg<128>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, extra, p);
   }
   count_launch();
   B200K_CHECK_LAUNCH("attn_fwd_bf16_tcgen05_kernel");

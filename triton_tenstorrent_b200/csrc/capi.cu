@@ -462,6 +462,15 @@ int b200k_attn_fwd_bf16(const void* q, const void* k, const void* v, void* o, fl
   return attn_fwd_bf16(a, static_cast<cudaStream_t>(stream));
 }
 
+int b200k_attn_fwd_bf16_multi(const void* q, const void* k, const void* v, void* const* o_dests, int n_dests,
+                              float* lse2, int Z, int H, int N_CTX, int D, int causal, float sm_scale, void* stream) {
+  clear_error();
+  if (o_dests == nullptr || n_dests < 1 || n_dests > 8)
+    return set_error(B200K_ERR_INVALID_ARG, "attn_multi: 1..8 destinations expected (got %d)", n_dests);
+  AttnArgs a{q, k, v, o_dests[0], lse2, Z, H, N_CTX, D, causal, sm_scale, o_dests + 1, n_dests - 1};
+  return attn_fwd_bf16(a, static_cast<cudaStream_t>(stream));
+}
+
 int b200k_attn_supported(int D, int N_CTX) { return attn_supported(D, N_CTX); }
 
 int b200k_launch(const char* kernel_name, int grid_x, int grid_y, int grid_z, void* stream, const b200k_arg* args,

@@ -48,6 +48,15 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
 // 64-byte swizzle, so the box lands as box_rows dense rows of 64 bytes.
 int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows);
 
+// Tensor maps of additional destinations of a kernel's output.  Every output tile is stored to the
+// caller's primary destination and to each of these, straight from the epilogue's staging buffer: the
+// destinations may be buffers of other GPUs mapped into this process (peer memory), which turns the
+// epilogue into the sending side of an all-gather that overlaps the main loop of the following tiles.
+constexpr int MAX_EXTRA_DESTS = 7;
+struct alignas(64) ExtraMaps {
+  CUtensorMap m[MAX_EXTRA_DESTS];
+};
+
 // Kernel launchers (one translation unit each).
 int add_f32(const float* x, const float* y, float* out, int64_t n, cudaStream_t s);
 int add_bf16(const uint16_t* x, const uint16_t* y, uint16_t* out, int64_t n, cudaStream_t s);
@@ -83,6 +92,8 @@ struct AttnArgs {
   int Z, H, N_CTX, D;
   int causal;
   float sm_scale;
+  void* const* extra_o;  // n_extra further [Z,H,N_CTX,D] destinations of O (host array of device pointers)
+  int n_extra;
 };
 int attn_fwd_bf16(const AttnArgs& a, cudaStream_t s);
 int attn_supported(int D, int N_CTX);

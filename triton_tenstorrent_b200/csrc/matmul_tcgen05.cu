@@ -61,14 +61,7 @@ struct MatmulParams {
   uint32_t* status;
 };
 
-// Tensor maps of additional destinations of C.  Every output tile is stored to the caller's C and to
-// each of these, straight from the epilogue's staging buffer: the destinations may be buffers of
-// other GPUs mapped into this process (peer memory), which turns the epilogue into the sending side
-// of an all-gather of C that overlaps the main loop of the following tiles.
-constexpr int MM_MAX_EXTRA = 7;
-struct alignas(64) ExtraMaps {
-  CUtensorMap m[MM_MAX_EXTRA];
-};
+constexpr int MM_MAX_EXTRA = MAX_EXTRA_DESTS;
 
 template <int BN, int STAGES>
 struct MatmulSmem {

@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_multi", "matmul_fused", "matmul_tma_fused", "attention",
+__all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_multi", "matmul_fused", "matmul_tma_fused", "attention", "attention_multi",
            "attention_with_lse", "device_status"]
 
 
@@ -407,6 +407,38 @@ def attention_with_lse(q, k, v, causal, sm_scale, warp_specialize: bool = True):
         _lib.check(lib.b200k_attn_fwd_bf16(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), M.data_ptr(),
                                            Z, H, N_CTX, D, 1 if causal else 0, float(sm_scale), _stream()))
     return _like_input(o, q), _like_input(M, q)
+
+
+def attention_multi(q, k, v, causal, sm_scale, out: torch.Tensor, remote_ptrs=()):
+    """O = attention(q, k, v) written by the kernel's epilogue into `out` (a contiguous bf16 [Z,H,N_CTX,D] tensor on
+    q's device, e.g. this rank's block of a larger buffer) and to every device address of `remote_ptrs` (the same
+    block inside other GPUs' buffers, mapped by sharding.GatheredRows); at most 8 destinations in all.  Returns
+    (out, M)."""
+    if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape:
+        raise ValueError("attention: q, k, v must be [Z, H, N_CTX, HEAD_DIM] with equal shapes")
+    if any(t.dtype != torch.bfloat16 or not t.is_cuda for t in (q, k, v, out)):
+        raise TypeError("attention_multi: bf16 CUDA tensors expected")
+    remote_ptrs = [int(p) for p in remote_ptrs]
+    if 1 + len(remote_ptrs) > 8:
+        raise ValueError("attention_multi: at most 8 destinations")
+    lib = _lib.load()
+    Z, H, N_CTX, D = q.shape
+    if not lib.b200k_attn_supported(D, N_CTX):
+        raise NotImplementedError(f"attention: no sm_100a kernel for HEAD_DIM={D}, N_CTX={N_CTX}")
+    if out.numel() != q.numel() or not out.is_contiguous() or out.device != q.device or out.data_ptr() % 16 != 0:
+        raise ValueError("attention_multi: out must be a contiguous block of Z*H*N_CTX*D bf16 elements on q's device")
+    for p in remote_ptrs:
+        if p == 0 or p % 16 != 0:
+            raise ValueError("attention_multi: remote destinations must be non-null and 16-byte aligned")
+    qd, kd, vd = (t.contiguous() for t in (q, k, v))
+    M = torch.empty((Z, H, N_CTX), device=qd.device, dtype=torch.float32)
+    all_ptrs = [out.data_ptr()] + remote_ptrs
+    ptrs = (ctypes.c_void_p * len(all_ptrs))(*all_ptrs)
+    with _on(qd.device):
+        _lib.check(lib.b200k_attn_fwd_bf16_multi(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ptrs, len(all_ptrs),
+                                                 M.data_ptr(), Z, H, N_CTX, D, 1 if causal else 0, float(sm_scale),
+                                                 _stream()))
+    return out, M
 
 
 def attention(q, k, v, causal, sm_scale, warp_specialize: bool = True) -> torch.Tensor:

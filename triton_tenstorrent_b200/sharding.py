@@ -111,3 +111,14 @@ def matmul_all_gather(a_shard, b, gathered: "GatheredRows", bias=None, activatio
                      remote_ptrs=gathered.remote_blocks())
     gathered.fence()
     return gathered.local
+
+
+def attention_all_gather(q_shard, k_shard, v_shard, causal, sm_scale, gathered: "GatheredRows"):
+    """Attention over this rank's (batch, head) shard ([Zs,Hs,N_CTX,D] with Zs*Hs*N_CTX == gathered.rows and
+    D == gathered.N) whose O tiles the kernel stores into every rank's copy of the full O; returns the local full O
+    as a [world * rows, D] matrix, complete after the fence."""
+    from . import ops
+    ops.attention_multi(q_shard, k_shard, v_shard, causal, sm_scale, gathered.own_block(),
+                        remote_ptrs=gathered.remote_blocks())
+    gathered.fence()
+    return gathered.local
