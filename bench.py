@@ -409,6 +409,14 @@ def secondary_workloads(torch, ops, gi, peaks, dist, world, rank, a, b, c, shard
         out[f"attention_fwd_{'causal' if causal else 'full'}"] = {"ms": ms, "TFLOP/s": t, "frac_of_burst_peak": t / tf,
                                                                  "frac_of_nominal_2250": t / 2250.0}
     del q, k, v
+    # the other head dimensions (same token count): 64 with twice the heads, 256 with half
+    for (Hh, Dh) in ((64, 64), (16, 256)):
+        q = torch.randn(Z, Hh, S, Dh, device="cuda").bfloat16()
+        k, v = torch.randn_like(q), torch.randn_like(q)
+        ms = quick_ms(lambda: ops.attention(q, k, v, False, Dh ** -0.5), torch, rep=10)
+        t = 4.0 * Z * Hh * S * S * Dh / ms / 1e9
+        out[f"attention_fwd_full_d{Dh}"] = {"ms": ms, "TFLOP/s": t, "frac_of_nominal_2250": t / 2250.0}
+        del q, k, v
 
     # matmul 4096^3 and 16384^3 (the other sizes of the workload definition)
     for S_ in (4096, 16384):

@@ -142,7 +142,7 @@ int b200k_matmul_tile32(const void* A, const void* B, void* C, int M, int N, int
 /*
  * O = softmax(Q K^T * sm_scale [+ causal mask]) V per (batch, head); q,k,v,o bf16 contiguous
  * [Z,H,N_CTX,D]; lse2[Z,H,N_CTX] fp32 receives m_i + log2(l_i) (base-2 log-sum-exp of the
- * scaled scores), exactly the `M` tensor of the reference.  D must be 64 or 128 and N_CTX a multiple of
+ * scaled scores), exactly the `M` tensor of the reference.  D must be 16, 32, 64, 128 or 256 (the reference's set, 06-fused-attention.py:233) and N_CTX a multiple of
  * 128 (b200k_attn_supported tells); the reference's other head sizes return B200K_ERR_UNSUPPORTED.
  * Replaces: _attn_fwd / _attn_fwd_inner, examples/fused-attn/06-fused-attention.py:33-90,143-215
  *           (host wrapper _attention.forward :224-273).

@@ -28,6 +28,9 @@ ATTN_CASES = [
     (1, 1, 384, 128, True, 128, 128),
     (1, 1, 128, 128, True, 32, 32),
     (1, 2, 128, 64, True, 64, 64),
+    (1, 2, 128, 16, True, 32, 16),
+    (1, 2, 128, 32, False, 64, 32),
+    (1, 1, 256, 256, True, 64, 64),
 ]
 
 

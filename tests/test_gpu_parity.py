@@ -496,9 +496,13 @@ def test_attention_rejects_unsupported():
     q = torch.zeros(1, 1, 100, 128, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(NotImplementedError):
         ops.attention(q, q, q, False, 0.1)
-    q32 = torch.zeros(1, 1, 128, 32, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(NotImplementedError):
-        ops.attention(q32, q32, q32, False, 0.1)
+    q48 = torch.zeros(1, 1, 128, 48, dtype=torch.bfloat16, device="cuda")       # not in {16, 32, 64, 128, 256}
+    with pytest.raises(AssertionError):
+        ops.attention(q48, q48, q48, False, 0.1)
+    lib = _lib.load()
+    rc = lib.b200k_attn_fwd_bf16(q48.data_ptr(), q48.data_ptr(), q48.data_ptr(), q48.data_ptr(), q48.data_ptr(), 1, 1, 128,
+                                 48, 0, 0.1, None)
+    assert rc == _lib.ERR_UNSUPPORTED
 
 
 @pytest.mark.parametrize("Z,H,S,causal", [(1, 2, 128, True), (2, 3, 512, False), (1, 4, 1024, True), (1, 1, 384, False)])
@@ -506,6 +510,19 @@ def test_attention_head_dim_64(Z, H, S, causal):
     D = 64
     q, k, v = gi.attn_inputs(Z, H, S, D, seed=24)
     ref_o, ref_m = oracle.attention(q, k, v, causal, D ** -0.5, BLOCK_M=128, BLOCK_N=64)   # BLOCK_N <= HEAD_DIM
+    o, m = ops.attention_with_lse(q.cuda(), k.cuda(), v.cuda(), causal, D ** -0.5)
+    assert float((o.cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
+    assert float((m.cpu() - ref_m).abs().max()) <= 1e-4
+
+
+@pytest.mark.parametrize("D,Z,H,S,causal", [(16, 1, 2, 128, True), (16, 2, 3, 640, False), (32, 1, 3, 384, True),
+                                            (32, 1, 2, 1024, False), (256, 1, 2, 128, True), (256, 1, 3, 384, True),
+                                            (256, 2, 2, 512, False)])
+def test_attention_other_head_dims(D, Z, H, S, causal):
+    # the reference's remaining head dimensions (06-fused-attention.py:233): 16 and 32 (box rows narrower than the
+    # swizzle span), 256 (one Q tile per CTA); BLOCK_N <= HEAD_DIM in the oracle as the reference asserts (:158)
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=27)
+    ref_o, ref_m = oracle.attention(q, k, v, causal, D ** -0.5, BLOCK_M=128, BLOCK_N=min(D, 128))
     o, m = ops.attention_with_lse(q.cuda(), k.cuda(), v.cuda(), causal, D ** -0.5)
     assert float((o.cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
     assert float((m.cpu() - ref_m).abs().max()) <= 1e-4

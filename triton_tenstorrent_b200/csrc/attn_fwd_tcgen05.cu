@@ -1,9 +1,9 @@
 // Fused attention forward for sm_100a: O = softmax(Q K^T * sm_scale [+ causal mask]) V, bf16 in/out,
-// HEAD_DIM 64 or 128, blockwise online softmax in the base-2 domain exactly like the reference kernel
+// HEAD_DIM 16, 32, 64, 128 or 256, blockwise online softmax in the base-2 domain exactly like the reference kernel
 // (examples/fused-attn/06-fused-attention.py:33-90 inner loop, :143-215 prologue/epilogue).
 //
-// One CTA owns a pair of adjacent 128-row Q tiles of one (batch, head) and walks the K/V blocks of
-// 128 keys once for both:
+// One CTA owns a pair of adjacent 128-row Q tiles of one (batch, head) (a single tile for HEAD_DIM 256,
+// where tensor memory and shared memory hold one) and walks the K/V blocks of 128 keys once for both:
 //   warps 0-3   softmax group of Q tile 0     warps 4-7   softmax group of Q tile 1
 //   warp 8      TMA producer (Q tiles, K/V ring of 32 KB slots in the order K0 V0 K1 V1 ...)
 //   warp 9      tensor-memory owner and tcgen05.mma issuer
@@ -34,22 +34,30 @@ namespace b200k {
 
 constexpr int AT_BM = 128;            // rows per Q tile
 constexpr int AT_BN = 128;            // keys per K/V block
-constexpr int AT_D_MAX = 128;         // head dimensions 64 and 128 are built
 constexpr int AT_THREADS = 384;         // three warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
 constexpr int AT_BOX_BYTES = 16384;   // one TMA box: 128 rows x 64 columns of bf16
-constexpr int AT_NSLOT = 5;           // K/V ring slots
-constexpr int AT_NBAR = 2 + 2 + 2 * AT_NSLOT + 2 + 2 + 2;
-// Shared-memory layout for head dimension D: Q0 | Q1 | K/V ring | barriers.  A 128 x D tile is D/64 boxes.
+constexpr int AT_MAX_NSLOT = 5;       // K/V ring slots (2 for head dimension 256)
+constexpr int AT_NBAR = 2 + 2 + 2 * AT_MAX_NSLOT + 2 + 2 + 2;
+// Shared-memory layout for head dimension D: Q0 | Q1 | K/V ring | barriers.  A 128 x D tile is
+// max(D/64, 1) boxes of 128 rows x 128 bytes.  For D < 64 a row only fills its first 2*D bytes: TMA pads
+// every box row to the 128-byte swizzle span, the MMAs and the TMA store touch only the filled part.
+// D = 256 leaves tensor memory (S 128 + O 256 columns) and shared memory for ONE Q tile per CTA.
 template <int D>
 struct AttnCfg {
-  static_assert(D == 64 || D == 128, "head dimension");
-  static constexpr int NBOX = D / 64;
-  static constexpr int TILE_BYTES = NBOX * AT_BOX_BYTES;   // 16 KB or 32 KB
+  static_assert(D == 16 || D == 32 || D == 64 || D == 128 || D == 256, "head dimension");
+  static constexpr int NBOX = D >= 64 ? D / 64 : 1;
+  static constexpr int BOX_COLS = D >= 64 ? 64 : D;        // elements per box row
+  static constexpr int TILE_BYTES = NBOX * AT_BOX_BYTES;   // footprint in shared memory: 16 .. 64 KB
+  static constexpr int TX_BYTES = AT_BM * D * 2;           // bytes a tile load delivers
+  static constexpr int NTILE = D <= 128 ? 2 : 1;           // Q tiles per CTA
+  static constexpr int NSLOT = D <= 128 ? AT_MAX_NSLOT : 2;
+  static constexpr int O_COL0 = NTILE * 128;               // first tensor-memory column of the O accumulators
   static constexpr int Q_OFF = 0;
-  static constexpr int KV_OFF = 2 * TILE_BYTES;
-  static constexpr int BAR_OFF = KV_OFF + AT_NSLOT * TILE_BYTES;
+  static constexpr int KV_OFF = NTILE * TILE_BYTES;
+  static constexpr int BAR_OFF = KV_OFF + NSLOT * TILE_BYTES;
   static constexpr int SMEM_TOTAL = BAR_OFF + AT_NBAR * 8 + 16 + 1024;
   static_assert(SMEM_TOTAL <= 232448, "attention shared memory budget exceeded");
+  static_assert(O_COL0 + NTILE * (D < 128 ? 128 : D) <= 512, "attention tensor memory budget exceeded");
 };
 
 constexpr float AT_RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -57,6 +65,7 @@ constexpr float AT_RESCALE_THRESHOLD = 8.0f;  // log2 units
 struct AttnParams {
   int ZH, N_CTX;
   int num_mblk, num_pairs, num_items;
+  int ntile;       // Q tiles per item (2, or 1 for head dimension 256)
   int causal;
   float qk_scale;  // sm_scale * 1.44269504 (fp32 product, as the reference computes it)
   float* lse2;
@@ -76,9 +85,9 @@ __device__ __forceinline__ AttnItem attn_item(const AttnParams& p, int item) {
   it.hz = item / p.num_pairs;
   int pr = item - it.hz * p.num_pairs;
   if (p.causal) pr = p.num_pairs - 1 - pr;  // longest rows first
-  it.mblk[0] = 2 * pr;
-  it.mblk[1] = 2 * pr + 1;
-  const bool valid1 = it.mblk[1] < p.num_mblk;
+  it.mblk[0] = p.ntile * pr;
+  it.mblk[1] = p.ntile * pr + 1;
+  const bool valid1 = p.ntile == 2 && it.mblk[1] < p.num_mblk;
   it.nblk[0] = p.causal ? it.mblk[0] + 1 : p.num_mblk;
   it.nblk[1] = valid1 ? (p.causal ? it.mblk[1] + 1 : p.num_mblk) : 0;
   it.n = it.nblk[1] > it.nblk[0] ? it.nblk[1] : it.nblk[0];
@@ -128,6 +137,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
   constexpr uint32_t IDESC_PV = umma_idesc_bf16_f32(AT_BM, D, 0, 1);      // P (TMEM) x V (N-major)
   using Cfg = AttnCfg<D>;
   constexpr int AT_TILE_BYTES = Cfg::TILE_BYTES;
+  constexpr int AT_NSLOT = Cfg::NSLOT;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -136,8 +146,8 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
   uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
   uint64_t* q_empty = q_full + 2;
   uint64_t* kv_full = q_empty + 2;
-  uint64_t* kv_empty = kv_full + AT_NSLOT;
-  uint64_t* s_full = kv_empty + AT_NSLOT;
+  uint64_t* kv_empty = kv_full + AT_MAX_NSLOT;
+  uint64_t* s_full = kv_empty + AT_MAX_NSLOT;
   uint64_t* p_full = s_full + 2;
   uint64_t* o_full = p_full + 2;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(o_full + 2);
@@ -194,7 +204,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           ok = mbar_wait(&q_empty[t], (q_loads[t] & 1u) ^ 1u, ctx, 10);
           if (!ok) break;
           if (lane == 0) {
-            mbar_expect_tx(&q_full[t], AT_TILE_BYTES);
+            mbar_expect_tx(&q_full[t], Cfg::TX_BYTES);
             const int row = row_base + it.mblk[t] * AT_BM;
 #pragma unroll
             for (int bx = 0; bx < Cfg::NBOX; ++bx)
@@ -208,7 +218,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         ok = mbar_wait(&kv_empty[slot], slot_phase ^ 1u, ctx, 11);
         if (!ok) break;
         if (lane == 0) {
-          mbar_expect_tx(&kv_full[slot], AT_TILE_BYTES);
+          mbar_expect_tx(&kv_full[slot], Cfg::TX_BYTES);
           const CUtensorMap* tm = is_v ? &tmap_v : &tmap_k;
           const int row = row_base + j * AT_BN;
           uint8_t* dst = smem_kv + slot * AT_TILE_BYTES;
@@ -254,7 +264,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         const uint64_t vd = v_desc0 + static_cast<uint64_t>((slot_idx * AT_TILE_BYTES) >> 4);
 #pragma unroll
         for (int k = 0; k < AT_BN / 16; ++k)
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, vd + static_cast<uint64_t>((k * 2048) >> 4),
+          umma_ts(tmem_base + Cfg::O_COL0 + t * 128, tmem_base + t * 128 + k * 8, vd + static_cast<uint64_t>((k * 2048) >> 4),
                   IDESC_PV, (accumulate || k > 0) ? 1u : 0u);
       }
       __syncwarp();
@@ -333,7 +343,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     const int r = q * 32 + static_cast<int>(lane);  // row within the tile
     const uint32_t lane_field = static_cast<uint32_t>(q * 32) << 16;
     const uint32_t t_s = tmem_base + lane_field + t * 128;        // S_t / P_t
-    const uint32_t t_o = tmem_base + lane_field + 256 + t * 128;  // O_t
+    const uint32_t t_o = tmem_base + lane_field + Cfg::O_COL0 + t * 128;  // O_t
     uint8_t* stage = smem_q + t * AT_TILE_BYTES;                  // O staging reuses the Q tile
     const float scale = p.qk_scale;
     uint32_t blk_cnt = 0, item_cnt = 0;
@@ -384,14 +394,23 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           l *= alpha;
           if (j > 0) {
             // the PV MMA of block j-1 has completed (its completion precedes s_full of block j)
+            if constexpr (D >= 32) {
 #pragma unroll 1
-            for (int c4 = 0; c4 < D / 32; ++c4) {
-              uint32_t o[32];
-              tmem_ld_x32(t_o + c4 * 32, o);
+              for (int c4 = 0; c4 < D / 32; ++c4) {
+                uint32_t o[32];
+                tmem_ld_x32(t_o + c4 * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                tmem_st_x32(t_o + c4 * 32, o);
+              }
+            } else {
+              uint32_t o[16];
+              tmem_ld_x16(t_o, o);
               tmem_wait_ld();
 #pragma unroll
-              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-              tmem_st_x32(t_o + c4 * 32, o);
+              for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+              tmem_st_x16(t_o, o);
             }
           }
         }
@@ -442,21 +461,37 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       ++item_cnt;
       tc_fence_after();
       const float inv_l = 1.0f / l;
+      if constexpr (D >= 32) {
 #pragma unroll 1
-      for (int c4 = 0; c4 < D / 32; ++c4) {
-        uint32_t o[32];
-        tmem_ld_x32(t_o + c4 * 32, o);
-        tmem_wait_ld();
-        uint8_t* row_ptr = stage + (c4 >> 1) * AT_BOX_BYTES + r * 128;
-        const int chunk0 = (c4 & 1) * 4;
+        for (int c4 = 0; c4 < D / 32; ++c4) {
+          uint32_t o[32];
+          tmem_ld_x32(t_o + c4 * 32, o);
+          tmem_wait_ld();
+          uint8_t* row_ptr = stage + (c4 >> 1) * AT_BOX_BYTES + r * 128;
+          const int chunk0 = (c4 & 1) * 4;
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
+          for (int jj = 0; jj < 4; ++jj) {
+            uint4 val;
+            val.x = pack_bf16x2(__uint_as_float(o[8 * jj + 0]) * inv_l, __uint_as_float(o[8 * jj + 1]) * inv_l);
+            val.y = pack_bf16x2(__uint_as_float(o[8 * jj + 2]) * inv_l, __uint_as_float(o[8 * jj + 3]) * inv_l);
+            val.z = pack_bf16x2(__uint_as_float(o[8 * jj + 4]) * inv_l, __uint_as_float(o[8 * jj + 5]) * inv_l);
+            val.w = pack_bf16x2(__uint_as_float(o[8 * jj + 6]) * inv_l, __uint_as_float(o[8 * jj + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(row_ptr + (((chunk0 + jj) ^ (r & 7)) << 4)) = val;
+          }
+        }
+      } else {
+        uint32_t o[16];
+        tmem_ld_x16(t_o, o);
+        tmem_wait_ld();
+        uint8_t* row_ptr = stage + r * 128;
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
           uint4 val;
           val.x = pack_bf16x2(__uint_as_float(o[8 * jj + 0]) * inv_l, __uint_as_float(o[8 * jj + 1]) * inv_l);
           val.y = pack_bf16x2(__uint_as_float(o[8 * jj + 2]) * inv_l, __uint_as_float(o[8 * jj + 3]) * inv_l);
           val.z = pack_bf16x2(__uint_as_float(o[8 * jj + 4]) * inv_l, __uint_as_float(o[8 * jj + 5]) * inv_l);
           val.w = pack_bf16x2(__uint_as_float(o[8 * jj + 6]) * inv_l, __uint_as_float(o[8 * jj + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(row_ptr + (((chunk0 + jj) ^ (r & 7)) << 4)) = val;
+          *reinterpret_cast<uint4*>(row_ptr + ((jj ^ (r & 7)) << 4)) = val;
         }
       }
       tc_fence_before();
@@ -492,7 +527,10 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
   }
 }
 
-int attn_supported(int D, int N_CTX) { return ((D == 64 || D == 128) && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0; }
+int attn_supported(int D, int N_CTX) {
+  const bool d_ok = D == 16 || D == 32 || D == 64 || D == 128 || D == 256;   // the reference's set (06-fused-attention.py:233)
+  return (d_ok && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0;
+}
 
 static int pick_grid(int sm_count, int num_items, int num_pairs, bool causal) {
   int grid = num_items < sm_count ? num_items : sm_count;
@@ -509,7 +547,7 @@ static int pick_grid(int sm_count, int num_items, int num_pairs, bool causal) {
 static int attn_check_args(const AttnArgs& a) {
   if (a.Z <= 0 || a.H <= 0 || a.N_CTX <= 0) return set_error(B200K_ERR_INVALID_ARG, "attention: Z, H, N_CTX must be positive");
   if (!attn_supported(a.D, a.N_CTX))
-    return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 64 or 128, N_CTX multiple of 128)", a.D, a.N_CTX);
+    return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 16, 32, 64, 128 or 256; N_CTX a multiple of 128)", a.D, a.N_CTX);
   if (a.q == nullptr || a.k == nullptr || a.v == nullptr || a.o == nullptr || a.lse2 == nullptr)
     return set_error(B200K_ERR_INVALID_ARG, "attention: null pointer");
   if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
@@ -532,20 +570,22 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
   CUtensorMap tq, tk, tv, to;
   int rc;
   const uint64_t D = static_cast<uint64_t>(a.D);
-  if ((rc = make_tmap_bf16_2d(&tq, a.q, D, rows, D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tk, a.k, D, rows, D, 64, AT_BN)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tv, a.v, D, rows, D, 64, AT_BN)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&to, a.o, D, rows, D, 64, 32)) != 0) return rc;
+  const uint32_t box_cols = a.D >= 64 ? 64u : static_cast<uint32_t>(a.D);
+  if ((rc = make_tmap_bf16_2d(&tq, a.q, D, rows, D, box_cols, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tk, a.k, D, rows, D, box_cols, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tv, a.v, D, rows, D, box_cols, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&to, a.o, D, rows, D, box_cols, 32)) != 0) return rc;
   ExtraMaps extra;
   memset(&extra, 0, sizeof(extra));
   for (int d = 0; d < a.n_extra; ++d)
-    if ((rc = make_tmap_bf16_2d(&extra.m[d], a.extra_o[d], D, rows, D, 64, 32)) != 0) return rc;
+    if ((rc = make_tmap_bf16_2d(&extra.m[d], a.extra_o[d], D, rows, D, box_cols, 32)) != 0) return rc;
 
   AttnParams p;
   p.ZH = a.Z * a.H;
   p.N_CTX = a.N_CTX;
   p.num_mblk = a.N_CTX / AT_BM;
-  p.num_pairs = (p.num_mblk + 1) / 2;
+  p.ntile = a.D <= 128 ? 2 : 1;
+  p.num_pairs = (p.num_mblk + p.ntile - 1) / p.ntile;
   p.num_items = p.ZH * p.num_pairs;
   p.causal = a.causal ? 1 : 0;
   p.qk_scale = a.sm_scale * 1.44269504f;
@@ -556,15 +596,22 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
   int grid = pick_grid(sm_count, p.num_items, p.num_pairs, p.causal != 0);
   if (const char* g = getenv("B200K_ATTN_GRID")) { int v = atoi(g); if (v > 0 && v <= p.num_items) grid = v; }
   // function attributes belong to the current context (per device); cheap enough to repeat
-  if (a.D == 64) {
-    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          AttnCfg<64>::SMEM_TOTAL));
-    attn_fwd_bf16_tcgen05_kernel<64><<<grid, AT_THREADS, AttnCfg<64>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, extra, p);
-  } else {
-    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          AttnCfg<128>::SMEM_TOTAL));
-    attn_fwd_bf16_tcgen05_kernel<128><<<grid, AT_THREADS, AttnCfg<128>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, extra, p);
+#define B200K_ATTN_LAUNCH(DD)                                                                                     \
+  case DD:                                                                                                        \
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_kernel<DD>,                                       \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<DD>::SMEM_TOTAL)); \
+    attn_fwd_bf16_tcgen05_kernel<DD><<<grid, AT_THREADS, AttnCfg<DD>::SMEM_TOTAL, stream>>>(tq, tk, tv, to, extra, p); \
+    break;
+  switch (a.D) {
+    B200K_ATTN_LAUNCH(16)
+    B200K_ATTN_LAUNCH(32)
+    B200K_ATTN_LAUNCH(64)
+    B200K_ATTN_LAUNCH(128)
+    B200K_ATTN_LAUNCH(256)
+    default:
+      return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d not built", a.D);
   }
+#undef B200K_ATTN_LAUNCH
   count_launch();
   B200K_CHECK_LAUNCH("attn_fwd_bf16_tcgen05_kernel");
   return B200K_OK;

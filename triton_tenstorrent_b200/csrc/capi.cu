@@ -132,7 +132,8 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
   if (encode == nullptr) return set_error(B200K_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld * 2) % 16 != 0)
     return set_error(B200K_ERR_INVALID_ARG, "tensor map: base and row pitch must be 16-byte aligned");
-  if (box_inner * 2 != 128 || box_outer == 0 || box_outer > 256)
+  // a box row narrower than the 128-byte swizzle span is padded to it in shared memory by TMA
+  if (box_inner == 0 || box_inner * 2 > 128 || (box_inner * 2) % 16 != 0 || box_outer == 0 || box_outer > 256)
     return set_error(B200K_ERR_INVALID_ARG, "tensor map: box %ux%u not supported", box_inner, box_outer);
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {ld * 2};

@@ -38,7 +38,8 @@ void count_launch();
   } while (0)
 
 // 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements,
-// box = box_inner x box_outer elements, 128-byte swizzle (box_inner * 2 bytes must be 128),
+// box = box_inner x box_outer elements, 128-byte swizzle (box_inner * 2 bytes at most 128; narrower rows are
+// padded to 128 bytes in shared memory),
 // out-of-bounds reads fill with zero.  Cached per (base, dims, pitch, box).
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer);

@@ -399,7 +399,7 @@ def attention_with_lse(q, k, v, causal, sm_scale, warp_specialize: bool = True):
     Z, H, N_CTX, D = q.shape
     if not lib.b200k_attn_supported(D, N_CTX):
         raise NotImplementedError(f"attention: no sm_100a kernel for HEAD_DIM={D}, N_CTX={N_CTX} "
-                                  "(HEAD_DIM 64 or 128 and N_CTX a multiple of 128 are built)")
+                                  "(N_CTX must be a multiple of 128)")
     qd, kd, vd = (_to_device(t).contiguous() for t in (q, k, v))
     o = torch.empty_like(qd)
     M = torch.empty((Z, H, N_CTX), device=qd.device, dtype=torch.float32)
