@@ -404,6 +404,43 @@ def test_attention_multi_destinations(D, causal):
         assert bool((f[:rows] == 7.5).all()) and bool((f[2 * rows:] == 7.5).all())
 
 
+def test_concurrent_threads_and_streams():
+    # the library is re-entrant: host threads with their own streams launch concurrently (tensor-map cache, error
+    # strings and the launch counter are shared or thread-local state) and every result equals the serial one
+    import threading
+    a, b = gi.matmul_inputs(512, 768, 640, seed=61)
+    q, k, v = gi.attn_inputs(1, 2, 256, 128, seed=61)
+    x, y = gi.add_inputs(1 << 18, seed=61)
+    ad, bd, qd, kd, vd, xd, yd = (t.cuda() for t in (a, b, q, k, v, x, y))
+    want = (ops.matmul_tma(ad, bd), ops.attention(qd, kd, vd, True, 0.09), ops.add(xd, yd))
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(idx):
+        try:
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for _ in range(20):
+                    got = (ops.matmul_tma(ad, bd), ops.attention(qd, kd, vd, True, 0.09), ops.add(xd, yd))
+                stream.synchronize()
+            for g, w in zip(got, want):
+                if not _bits_equal(g.float(), w.float()):
+                    errors.append(f"thread {idx}: result differs")
+            try:
+                ops.matmul_tma(ad, bd[:100])          # K mismatch: an error on this thread only
+            except AssertionError:
+                pass
+        except Exception as e:  # noqa: BLE001
+            errors.append(f"thread {idx}: {e!r}")
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+
+
 def test_cuda_graph_capture_and_replay():
     # the launch-bound calls (the reference's own add at n = 98432 is one) can be recorded once and replayed: every
     # entry point launches on the caller's stream and neither allocates nor synchronises once the device is warm

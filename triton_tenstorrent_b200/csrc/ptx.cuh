@@ -94,7 +94,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA (tiled, 2-D and 3-D; loads complete on an mbarrier, stores use bulk groups).  No multicast.
+// TMA (tiled, 2-D and 4-D; loads complete on an mbarrier, stores use bulk groups).  No multicast.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
