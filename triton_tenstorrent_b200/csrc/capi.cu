@@ -154,9 +154,10 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return B200K_OK;
 }
 
-int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows) {
+int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows,
+                     bool row_pairs) {
   const uint32_t box_cols = 32;
-  TmapKey key{reinterpret_cast<uintptr_t>(base), cols, rows, 0, box_cols, box_rows, 1};
+  TmapKey key{reinterpret_cast<uintptr_t>(base), cols, rows, 0, box_cols, box_rows, row_pairs ? 2u : 1u};
   {
     std::lock_guard<std::mutex> lock(g_tmap_mutex);
     auto it = g_tmaps.find(key);
@@ -175,13 +176,20 @@ int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t
   if (box_rows == 0 || (box_rows & 31) || box_rows > 256)
     return set_error(B200K_ERR_INVALID_ARG, "tile-major tensor map: box %u x %u not supported", box_rows, box_cols);
   const uint64_t tile_bytes = 32 * 32 * 2;
+  // (column in tile, tile column, row in tile, tile row); with row_pairs the two rows of a pair form one
+  // 128-byte line: (element in line, tile column, line in tile, tile row)
   cuuint64_t dims[4] = {32, cols / 32, 32, rows / 32};
   cuuint64_t strides[3] = {tile_bytes, 32 * 2, (cols / 32) * tile_bytes};  // next tile column, next row in tile, next tile row
   cuuint32_t box[4] = {32, 1, 32, box_rows / 32};
+  if (row_pairs) {
+    dims[0] = 64; dims[2] = 16;
+    strides[1] = 64 * 2;
+    box[0] = 64; box[2] = 16;
+  }
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, row_pairs ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return set_error(B200K_ERR_CUDA, "cuTensorMapEncodeTiled (tile-major) failed with CUresult %d (%llu x %llu, box %u x %u)",
                      static_cast<int>(r), (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);

@@ -47,7 +47,12 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
 // row-major order; rows and cols multiples of 32): dimensions (column in tile, tile column, row in
 // tile, tile row), box = box_rows x 32 elements (one tile column, box_rows a multiple of 32),
 // 64-byte swizzle, so the box lands as box_rows dense rows of 64 bytes.
-int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows);
+// row_pairs: the two 64-byte rows of a pair are fetched as ONE 128-byte line (half as many requests to
+// L2) with the 128-byte swizzle.  Read back as a 64-byte-swizzled image this is the same data except that
+// rows r and r ^ 1 have changed places wherever bit 3 of r is set (the two swizzles differ in address bit 9
+// only): usable for the K-major A operand, whose row order only permutes the rows of the accumulator.
+int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows,
+                     bool row_pairs = false);
 
 // Tensor maps of additional destinations of a kernel's output.  Every output tile is stored to the
 // caller's primary destination and to each of these, straight from the epilogue's staging buffer: the

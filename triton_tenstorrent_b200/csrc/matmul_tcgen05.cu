@@ -182,11 +182,14 @@ __device__ __forceinline__ void epilogue_chunk(const MatmulParams& p, const CUte
     __syncwarp();
     uint8_t* stage_buf = my_stage + buf * MM_C_BUF_BYTES;
     if (p.tile32) {
-      // two 32 x 32 tiles side by side, each 32 rows of 64 bytes with the 64-byte swizzle
+      // two 32 x 32 tiles side by side, each 32 rows of 64 bytes with the 64-byte swizzle.  A was fetched as
+      // 128-byte row pairs (make_tmap_tile32, row_pairs): accumulator row r holds the result row r ^ 1 wherever
+      // bit 3 of r is set, which is undone here by the choice of the staging row.
+      const uint32_t srow = lane ^ ((lane >> 3) & 1u);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const uint4 val = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-        *reinterpret_cast<uint4*>(stage_buf + (j >> 2) * 2048 + lane * 64 + (((j & 3) ^ ((lane >> 1) & 3)) << 4)) = val;
+        *reinterpret_cast<uint4*>(stage_buf + (j >> 2) * 2048 + srow * 64 + (((j & 3) ^ ((srow >> 1) & 3)) << 4)) = val;
       }
     } else {
       uint8_t* dst = stage_buf + lane * 128;
@@ -617,7 +620,7 @@ static int make_operand_tmaps(const MatmulArgs& a, CUtensorMap* ta, CUtensorMap*
   for (int d = 0; d < a.n_extra; ++d)
     if ((rc = make_tmap_bf16_2d(&extra->m[d], a.extra_C[d], a.N, a.M, a.ldc, 64, 32)) != 0) return rc;
   if (a.tile32) {
-    if ((rc = make_tmap_tile32(ta, a.A, a.K, a.M, MM_BM)) != 0) return rc;
+    if ((rc = make_tmap_tile32(ta, a.A, a.K, a.M, MM_BM, /*row_pairs=*/true)) != 0) return rc;
     if ((rc = make_tmap_tile32(tb, a.B, a.N, a.K, MM_BK)) != 0) return rc;
     return make_tmap_tile32(tc, a.C, a.N, a.M, 32);
   }
