@@ -239,6 +239,17 @@ int b200k_ipc_export(const void* ptr, b200k_ipc_handle* out);
 int b200k_ipc_open(const b200k_ipc_handle* h, void** ptr);
 
 /*
+ * The static schedule of a causal attention launch, for inspection and tests (pure host arithmetic, no device):
+ * Z*H heads, N_CTX rows, head dimension D, `ctas` CTAs.  Items are (head, pair of 128-row Q tiles), numbered
+ * head * pairs + level with level 0 the longest row position; table[k * ctas + c] is the item CTA c
+ * processes k-th (-1 = none).  *rounds receives the number of rows of the table; fails with
+ * B200K_ERR_INVALID_ARG when `capacity` (in ints) is too small.  The reference leaves this to its persistent
+ * block loop over equal blocks (cpu/lib/Dialect/TritonCPU/Transforms/MakePersistentKernel.cpp:144-198); causal
+ * attention items are not equal, hence a work-queue order instead of equal ranges.
+ */
+int b200k_attn_causal_schedule(int ZH, int N_CTX, int D, int ctas, int* table, int capacity, int* rounds);
+
+/*
  * Contiguous block range of worker `w` out of `workers` over `num_blocks` blocks:
  * base = nb / W, rem = nb % W, worker w gets [w*base + min(w,rem), +base + (w<rem)).
  * Replaces: the per-core partition of npu/lib/TritonNPUToTenstorrent/D2M/SPMDOpToD2M.cpp:53-113.

@@ -198,3 +198,41 @@ def test_ops_fail_loudly_without_cuda():
         pytest.skip("a GPU is present")
     with pytest.raises(Exception):
         ops.add(torch.zeros(8), torch.zeros(8))
+
+
+@pytest.mark.parametrize("ZH,S,D,ctas", [(128, 4096, 128, 148), (3, 384, 128, 148), (16, 2048, 256, 148), (40, 8192, 64, 132),
+                                         (1, 128, 128, 148)])
+def test_causal_attention_schedule_covers_and_balances(ZH, S, D, ctas):
+    # every (head, row pair) item exactly once; per-CTA work (K/V blocks + 1 per item) within one longest item of the mean
+    import ctypes
+    lib = _lib.load()
+    ntile = 2 if D <= 128 else 1
+    mblk = S // 128
+    pairs = -(-mblk // ntile)
+    items = ZH * pairs
+    ctas = min(ctas, items)
+    cap = (items + ctas) * 2
+    table = (ctypes.c_int * cap)()
+    rounds = ctypes.c_int()
+    assert lib.b200k_attn_causal_schedule(ZH, S, D, ctas, table, cap, ctypes.byref(rounds)) == _lib.OK
+    t = [table[i] for i in range(rounds.value * ctas)]
+    seen = sorted(x for x in t if x >= 0)
+    assert seen == list(range(items))
+
+    def blocks(item):
+        pr = pairs - 1 - item % pairs
+        m0, m1 = ntile * pr, ntile * pr + 1
+        return max(m0 + 1, m1 + 1 if (ntile == 2 and m1 < mblk) else 0) + 1
+
+    load = [sum(blocks(t[k * ctas + c]) for k in range(rounds.value) if t[k * ctas + c] >= 0) for c in range(ctas)]
+    mean = sum(load) / ctas
+    assert max(load) <= mean + blocks(0)              # list scheduling: at most one (longest) item above the mean
+    if items >= 8 * ctas:
+        assert max(load) <= 1.05 * mean               # many items per CTA: within 5 %
+    # items are taken head by head (which keeps concurrently running CTAs on the same few heads) except for the last
+    # one and a half rounds, which are taken longest first
+    tail_heads = min(ZH, -(-(3 * ctas // 2) // pairs))
+    for c in range(ctas):
+        mine = [x for x in (t[k * ctas + c] for k in range(rounds.value)) if 0 <= x < (ZH - tail_heads) * pairs]
+        assert mine == sorted(mine)
+    assert lib.b200k_attn_causal_schedule(ZH, S, D, ctas, table, 0, ctypes.byref(rounds)) == _lib.ERR_INVALID_ARG

@@ -83,6 +83,7 @@ SIGNATURES = {
                                             c_float, c_void_p]),
     "b200k_attn_fwd_bf16_multi": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int, c_void_p, c_int, c_int,
                                           c_int, c_int, c_int, c_float, c_void_p]),
+    "b200k_attn_causal_schedule": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int), c_int, POINTER(c_int)]),
     "b200k_attn_supported": (c_int, [c_int, c_int]),
     "b200k_launch": (c_int, [c_char_p, c_int, c_int, c_int, c_void_p, POINTER(Arg), c_int]),
     "b200k_device_props": (c_int, [c_int, POINTER(Props)]),

@@ -25,7 +25,12 @@
 #include <string.h>
 
 #include <atomic>
+#include <map>
 #include <mutex>
+#include <queue>
+#include <tuple>
+#include <utility>
+#include <vector>
 
 #include "launch.h"
 #include "ptx.cuh"
@@ -65,6 +70,8 @@ constexpr float AT_RESCALE_THRESHOLD = 8.0f;  // log2 units
 struct AttnParams {
   int ZH, N_CTX;
   int num_mblk, num_pairs, num_items;
+  int rounds;        // items per CTA (the longest list)
+  const int* sched;  // [rounds][grid] item of CTA c in round k (-1 = none); nullptr: item k * grid + c
   int ntile;       // Q tiles per item (2, or 1 for head dimension 256)
   int causal;
   float qk_scale;  // sm_scale * 1.44269504 (fp32 product, as the reference computes it)
@@ -92,6 +99,14 @@ __device__ __forceinline__ AttnItem attn_item(const AttnParams& p, int item) {
   it.nblk[1] = valid1 ? (p.causal ? it.mblk[1] + 1 : p.num_mblk) : 0;
   it.n = it.nblk[1] > it.nblk[0] ? it.nblk[1] : it.nblk[0];
   return it;
+}
+
+// The item of this CTA in round k, or -1.  Causal launches read a table made by the host (a list schedule that
+// balances the unequal item lengths, see attn_schedule); otherwise items are strided over the CTAs.
+__device__ __forceinline__ int attn_round_item(const AttnParams& p, int k) {
+  const int idx = k * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
+  const int item = p.sched != nullptr ? __ldg(p.sched + idx) : idx;
+  return item < p.num_items ? item : -1;
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -194,7 +209,9 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     uint32_t slot_phase = 0;
     uint32_t q_loads[2] = {0, 0};
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+    for (int round = 0; ok && round < p.rounds; ++round) {
+      const int item = attn_round_item(p, round);
+      if (item < 0) continue;
       const AttnItem it = attn_item(p, item);
       const int row_base = it.hz * p.N_CTX;
       for (int step = 0; ok && step < 2 * it.n; ++step) {
@@ -270,7 +287,9 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       __syncwarp();
     };
 
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+    for (int round = 0; ok && round < p.rounds; ++round) {
+      const int item = attn_round_item(p, round);
+      if (item < 0) continue;
       const AttnItem it = attn_item(p, item);
       // ---- block 0 scores
       ok = mbar_wait(&kv_full[slot], slot_phase, ctx, 20);
@@ -348,7 +367,9 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     const float scale = p.qk_scale;
     uint32_t blk_cnt = 0, item_cnt = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+    for (int round = 0; ok && round < p.rounds; ++round) {
+      const int item = attn_round_item(p, round);
+      if (item < 0) continue;
       const AttnItem it = attn_item(p, item);
       const int n_me = it.nblk[t];
       if (n_me == 0) continue;
@@ -564,8 +585,82 @@ static int attn_check_args(const AttnArgs& a) {
   return B200K_OK;
 }
 
+// Causal items differ in length (2 to 2 * num_pairs K/V blocks), so dealing them out with a fixed stride leaves
+// some CTAs with up to 12 % more work than the average.  The host instead simulates a work queue: items are taken
+// in launch order (head by head, longest row position first, so that the CTAs running at the same time share
+// the K/V of a few heads in L2) by whichever CTA becomes free first.  The resulting table [rounds][grid] lives in
+// device memory, one per (shape, grid, device), created at the first launch of that shape.
+struct SchedKey {
+  int device, ZH, num_pairs, num_mblk, ntile, grid;
+  bool operator<(const SchedKey& o) const {
+    return std::tie(device, ZH, num_pairs, num_mblk, ntile, grid) <
+           std::tie(o.device, o.ZH, o.num_pairs, o.num_mblk, o.ntile, o.grid);
+  }
+};
+struct SchedTable {
+  int* dev;
+  int rounds;
+};
+static std::map<SchedKey, SchedTable> g_sched;
+static std::mutex g_sched_mutex;
+
+// Host mirror of attn_item's block count for a causal item.
+static int causal_item_blocks(int item, int num_pairs, int num_mblk, int ntile) {
+  const int pr = num_pairs - 1 - item % num_pairs;
+  const int m0 = ntile * pr, m1 = ntile * pr + 1;
+  const int n1 = (ntile == 2 && m1 < num_mblk) ? m1 + 1 : 0;
+  return n1 > m0 + 1 ? n1 : m0 + 1;
+}
+
+std::vector<int> attn_schedule(int ZH, int num_pairs, int num_mblk, int ntile, int grid, int* rounds_out) {
+  const int num_items = ZH * num_pairs;
+  std::vector<std::vector<int>> lists(grid);
+  // (time at which the CTA is free, CTA): smallest first
+  std::priority_queue<std::pair<double, int>, std::vector<std::pair<double, int>>, std::greater<std::pair<double, int>>> free_at;
+  for (int c = 0; c < grid; ++c) free_at.push({0.0, c});
+  // Launch order: head by head, longest row position first; the items of the last few heads (about one and a half
+  // rounds) are merged and taken longest first across those heads, so that the queue ends with the shortest items.
+  std::vector<int> order;
+  order.reserve(num_items);
+  int tail_heads = (3 * grid / 2 + num_pairs - 1) / num_pairs;
+  if (tail_heads > ZH) tail_heads = ZH;
+  for (int item = 0; item < (ZH - tail_heads) * num_pairs; ++item) order.push_back(item);
+  for (int level = 0; level < num_pairs; ++level)
+    for (int hz = ZH - tail_heads; hz < ZH; ++hz) order.push_back(hz * num_pairs + level);
+  for (int item : order) {
+    auto [t, c] = free_at.top();
+    free_at.pop();
+    lists[c].push_back(item);
+    // one period per K/V block plus about one for loading Q, the first scores and the epilogue
+    free_at.push({t + causal_item_blocks(item, num_pairs, num_mblk, ntile) + 1.0, c});
+  }
+  size_t rounds = 0;
+  for (const auto& l : lists) rounds = l.size() > rounds ? l.size() : rounds;
+  std::vector<int> table(rounds * grid, -1);
+  for (int c = 0; c < grid; ++c)
+    for (size_t k = 0; k < lists[c].size(); ++k) table[k * grid + c] = lists[c][k];
+  *rounds_out = static_cast<int>(rounds);
+  return table;
+}
+
+static int get_schedule(const SchedKey& key, const int** dev_table, int* rounds) {
+  std::lock_guard<std::mutex> lock(g_sched_mutex);
+  auto it = g_sched.find(key);
+  if (it == g_sched.end()) {
+    int r = 0;
+    const std::vector<int> table = attn_schedule(key.ZH, key.num_pairs, key.num_mblk, key.ntile, key.grid, &r);
+    int* dev = nullptr;
+    B200K_CHECK_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), table.size() * sizeof(int)));
+    B200K_CHECK_CUDA(cudaMemcpy(dev, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice));
+    it = g_sched.emplace(key, SchedTable{dev, r}).first;
+  }
+  *dev_table = it->second.dev;
+  *rounds = it->second.rounds;
+  return B200K_OK;
+}
+
 // Encodes the tensor maps and launches the kernel on `sm_count` SMs, reporting to `status`.
-static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uint32_t* status) {
+static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uint32_t* status, bool may_allocate) {
   const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
   CUtensorMap tq, tk, tv, to;
   int rc;
@@ -595,6 +690,15 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
 
   int grid = pick_grid(sm_count, p.num_items, p.num_pairs, p.causal != 0);
   if (const char* g = getenv("B200K_ATTN_GRID")) { int v = atoi(g); if (v > 0 && v <= p.num_items) grid = v; }
+  p.sched = nullptr;
+  p.rounds = (p.num_items + grid - 1) / grid;
+  const char* sched_env = getenv("B200K_ATTN_SCHEDULE");
+  if (p.causal && p.num_pairs > 1 && may_allocate && !(sched_env != nullptr && atoi(sched_env) == 0)) {
+    grid = p.num_items < sm_count ? p.num_items : sm_count;   // the table balances any grid: use every SM
+    int dev = 0;
+    B200K_CHECK_CUDA(cudaGetDevice(&dev));
+    if ((rc = get_schedule(SchedKey{dev, p.ZH, p.num_pairs, p.num_mblk, p.ntile, grid}, &p.sched, &p.rounds)) != 0) return rc;
+  }
   // function attributes belong to the current context (per device); cheap enough to repeat
 #define B200K_ATTN_LAUNCH(DD)                                                                                     \
   case DD:                                                                                                        \
@@ -623,7 +727,7 @@ int attn_fwd_bf16(const AttnArgs& a, cudaStream_t stream) {
   const DeviceInfo* dev = current_device_info();
   if (dev == nullptr) return B200K_ERR_NO_DEVICE;
   if (dev->cc_major != 10) return set_error(B200K_ERR_NO_DEVICE, "attention: needs an sm_100 device (found sm_%d%d)", dev->cc_major, dev->cc_minor);
-  return attn_launch(a, stream, dev->sm_count, dev->status_word);
+  return attn_launch(a, stream, dev->sm_count, dev->status_word, /*may_allocate=*/true);
 }
 
 }  // namespace b200k
@@ -708,6 +812,6 @@ extern "C" int b200k_attn_fwd_bf16_noalloc(const void* q, const void* k, const v
   // statistics are write-only and need no clearing
   B200K_CHECK_CUDA(cudaMemsetAsync(dev->scratch, 0, 64 * sizeof(uint32_t), s));
   a.lse2 = reinterpret_cast<float*>(dev->scratch + 64);
-  return attn_launch(a, s, dev->sm_count, dev->scratch);
+  return attn_launch(a, s, dev->sm_count, dev->scratch, /*may_allocate=*/false);  // strided items, no schedule table
 }
 

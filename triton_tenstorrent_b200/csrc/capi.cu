@@ -480,6 +480,22 @@ int b200k_attn_fwd_bf16_multi(const void* q, const void* k, const void* v, void*
   return attn_fwd_bf16(a, static_cast<cudaStream_t>(stream));
 }
 
+int b200k_attn_causal_schedule(int ZH, int N_CTX, int D, int ctas, int* table, int capacity, int* rounds) {
+  clear_error();
+  if (ZH <= 0 || ctas <= 0 || table == nullptr || rounds == nullptr || !attn_supported(D, N_CTX))
+    return set_error(B200K_ERR_INVALID_ARG, "attn_causal_schedule: bad arguments");
+  const int ntile = D <= 128 ? 2 : 1;
+  const int num_mblk = N_CTX / 128;
+  const int num_pairs = (num_mblk + ntile - 1) / ntile;
+  int r = 0;
+  const std::vector<int> t = attn_schedule(ZH, num_pairs, num_mblk, ntile, ctas, &r);
+  if (static_cast<size_t>(capacity) < t.size())
+    return set_error(B200K_ERR_INVALID_ARG, "attn_causal_schedule: table needs %zu ints", t.size());
+  memcpy(table, t.data(), t.size() * sizeof(int));
+  *rounds = r;
+  return B200K_OK;
+}
+
 int b200k_attn_supported(int D, int N_CTX) { return attn_supported(D, N_CTX); }
 
 int b200k_launch(const char* kernel_name, int grid_x, int grid_y, int grid_z, void* stream, const b200k_arg* args,

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <vector>
+
 #include "../../include/b200k.h"
 
 namespace b200k {
@@ -103,6 +105,9 @@ struct AttnArgs {
 };
 int attn_fwd_bf16(const AttnArgs& a, cudaStream_t s);
 int attn_supported(int D, int N_CTX);
+// Work-queue simulation that assigns the causal items (ZH * num_pairs, head-major, longest first) to `grid` CTAs:
+// returns the table [rounds][grid] of item numbers (-1 = none).  Pure host code.
+std::vector<int> attn_schedule(int ZH, int num_pairs, int num_mblk, int ntile, int grid, int* rounds_out);
 int selftest_wait_timeout(long long budget_cycles, cudaStream_t s);
 
 }  // namespace b200k
