@@ -75,19 +75,37 @@ class GatheredRows:
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         lib = _lib.load()
         mine = _lib.IpcHandle()
+        # A failure on one rank (IPC not permitted, no peer access) must not leave the others waiting in a collective:
+        # every step's outcome is exchanged and all ranks raise together.
         with torch.cuda.device(device):
-            _lib.check(lib.b200k_ipc_export(self.local.data_ptr(), ctypes.byref(mine)))
+            problem = ""
+            try:
+                _lib.check(lib.b200k_ipc_export(self.local.data_ptr(), ctypes.byref(mine)))
+            except Exception as e:  # noqa: BLE001
+                problem = f"rank {self.rank}: {e}"
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(mine), group=group)
+            dist.all_gather_object(handles, (bytes(mine), problem), group=group)
+            problems = [p for _, p in handles if p]
+            if problems:
+                raise RuntimeError("GatheredRows: exporting the buffers failed: " + "; ".join(problems))
             self.copy_ptrs = []
-            for r, raw in enumerate(handles):
+            for r, (raw, _) in enumerate(handles):
                 if r == self.rank:
                     self.copy_ptrs.append(self.local.data_ptr())
                     continue
                 h = _lib.IpcHandle.from_buffer_copy(raw)
                 p = ctypes.c_void_p()
-                _lib.check(lib.b200k_ipc_open(ctypes.byref(h), ctypes.byref(p)))
+                try:
+                    _lib.check(lib.b200k_ipc_open(ctypes.byref(h), ctypes.byref(p)))
+                except Exception as e:  # noqa: BLE001
+                    problem = f"rank {self.rank} opening rank {r}: {e}"
+                    break
                 self.copy_ptrs.append(p.value)
+            outcomes = [None] * self.world
+            dist.all_gather_object(outcomes, problem, group=group)
+            problems = [p for p in outcomes if p]
+            if problems:
+                raise RuntimeError("GatheredRows: mapping the peers' buffers failed: " + "; ".join(problems))
 
     def own_block(self):
         """This rank's rows inside its own copy (a tensor view)."""
