@@ -362,6 +362,22 @@ def test_matmul_tile32_oracle_shapes(shape, dtype):
         assert torch.equal(ops.untilize(got).view(torch.int16), row.view(torch.int16))
 
 
+def test_matmul_tile32_full_size_equals_row_major():
+    # the workload's full size through the CTA-pair kernel: tile-major in / out equals the row-major result bit for
+    # bit (both layouts feed the same MMAs; the row-pair fetch of A only permutes accumulator rows, undone in the epilogue)
+    S = 8192
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = (torch.randn(S, S, device="cuda", generator=g) / S ** 0.5).bfloat16()
+    b = (torch.randn(S, S, device="cuda", generator=g) / S ** 0.5).bfloat16()
+    row = ops.matmul(a, b, "leaky_relu")
+    tiled = ops.matmul(ops.tilize(a), ops.tilize(b), "leaky_relu", layout="tile32")
+    assert torch.equal(ops.untilize(tiled).view(torch.int16), row.view(torch.int16))
+    # a sample of rows against the CPU oracle
+    rows = torch.tensor([0, 1, 8, 9, 15, 31, 127, 128, 4095, 8191])
+    ref = oracle.golden_matmul(a[rows].cpu(), b.cpu(), activation="leaky_relu")
+    assert oracle.rel_frobenius(row[rows.cuda()].cpu().float(), ref.float()) <= MATMUL_REL_FRO
+
+
 def test_matmul_tile32_rejects_bad_arguments():
     t = torch.zeros(64, 64, dtype=torch.float16, device="cuda")
     with pytest.raises(ValueError):
