@@ -193,6 +193,29 @@ def test_matmul_cta_pair_kernel_tails(shape):
     assert oracle.rel_frobenius(got.float(), oracle.golden_matmul(a, b, bias=bias_full, mode=2).float()) <= MATMUL_REL_FRO
 
 
+@pytest.mark.parametrize("shape", [(4096, 4096, 192), (2560, 4096, 320), (4352, 4608, 136)])
+def test_matmul_split_last_wave(shape, monkeypatch):
+    # tile counts whose last wave fills at most half of the CTA pairs: its tiles are computed as two 256 x 128 halves.
+    # Same MMAs over K in the same order, so the result equals the unsplit schedule bit for bit; rows against the oracle.
+    M, N, K = shape
+    props = torch.cuda.get_device_properties(0)
+    pairs = props.multi_processor_count // 2
+    tiles = -(-M // 256) * -(-N // 256)
+    if not (tiles >= pairs and 0 < tiles % pairs <= pairs // 2):
+        pytest.skip("this device's SM count does not give a sparse last wave for the shape")
+    a, b = gi.matmul_inputs(M, N, K, seed=71)
+    bias = gi.row_bias(N).cuda()
+    ad, bd = a.cuda(), b.cuda()
+    split = ops.matmul_fused(ad, bd, bias, "relu")
+    monkeypatch.setenv("B200K_MATMUL_SPLIT_TAIL", "0")
+    whole = ops.matmul_fused(ad, bd, bias, "relu")
+    monkeypatch.delenv("B200K_MATMUL_SPLIT_TAIL")
+    assert torch.equal(split.view(torch.int16), whole.view(torch.int16))
+    rows = torch.tensor([0, 255, 256, M // 2 + 3, M - 257, M - 1])
+    ref = oracle.golden_matmul(a[rows], b, bias=bias.cpu(), mode=3, activation="relu")
+    assert oracle.rel_frobenius(split[rows.cuda()].cpu().float(), ref.float()) <= MATMUL_REL_FRO
+
+
 def test_matmul_strided_operands_and_canaries():
     M, N, K = 300, 200, 264
     a, b = gi.matmul_inputs(M, N, K, seed=4)

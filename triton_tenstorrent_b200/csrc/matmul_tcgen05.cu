@@ -42,6 +42,10 @@ struct MatmulParams {
   int M, N, K;
   int num_pid_m, num_pid_n, group_m;
   int num_tiles, num_kb;
+  // CTA-pair kernel: work items [0, full_work) are whole 256 x 256 tiles; items beyond are the tiles of the last,
+  // less than half full wave cut in two 256 x 128 halves, so that twice as many pairs share it (num_work items in all)
+  int num_work, full_work;
+  uint32_t idesc_half;             // instruction descriptor of the 256 x 128 MMA
   const float* bias_row;      // [N] fp32 or nullptr
   const uint16_t* bias_full;  // [M, ldbias] bf16 or nullptr
   int64_t ldbias;
@@ -390,6 +394,26 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
 // release the ring slot in both CTAs and publish the accumulator to both epilogues.
 // =============================================================================================
 constexpr int MM2_BN = 256;                                  // tile columns (both CTAs)
+
+struct PairWork {
+  int pid_m, pid_n;
+  int col0;    // first column of the work item
+  int width;   // 256, or 128 for a half tile
+};
+__device__ __forceinline__ PairWork pair_work(const MatmulParams& p, int w) {
+  PairWork r;
+  int tile = w, half = 0;
+  r.width = MM2_BN;
+  if (w >= p.full_work) {
+    const int t = w - p.full_work;
+    tile = p.full_work + (t >> 1);
+    half = t & 1;
+    r.width = MM2_BN / 2;
+  }
+  tile_coords(p, tile, r.pid_m, r.pid_n);
+  r.col0 = r.pid_n * MM2_BN + half * (MM2_BN / 2);
+  return r;
+}
 constexpr int MM2_B_STAGE_BYTES = 2 * MM_B_BOX_BYTES;        // this CTA's 64 x 128 half of B: 16 KB
 constexpr int MM2_STAGE_BYTES = MM_A_STAGE_BYTES + MM2_B_STAGE_BYTES;  // 32 KB per CTA per K block
 
@@ -465,30 +489,28 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
     // The A row panel of a tile group is re-read by every tile column of the sweep; B tiles stream.
     const uint64_t pol_a = p.l2_hint ? l2_policy_evict_last() : l2_policy_evict_normal();
     const uint64_t pol_b = p.l2_hint == 1 ? l2_policy_evict_first() : l2_policy_evict_normal();
-    for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
-      int pid_m, pid_n;
-      tile_coords(p, tile, pid_m, pid_n);
-      const int m0 = pid_m * 256 + static_cast<int>(rank) * MM_BM;
-      const int n0 = pid_n * MM2_BN + static_cast<int>(rank) * 128;
+    for (int work = pair; ok && work < p.num_work; work += num_pairs) {
+      const PairWork wk = pair_work(p, work);
+      const int m0 = wk.pid_m * 256 + static_cast<int>(rank) * MM_BM;
+      const int n0 = wk.col0 + static_cast<int>(rank) * (wk.width / 2);   // this CTA's half of the item's columns
+      const int b_boxes = wk.width / 128;                                  // 64-column boxes this CTA loads
       for (int kb = 0; kb < p.num_kb; ++kb) {
         ok = mbar_wait(&empty_bar[stage], phase ^ 1u, ctx, 41);
         if (!ok) break;
         if (lane == 0) {
           const uint32_t leader_full = mapa_shared(smem_u32(&full_bar[stage]), 0);
-          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * MM2_STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * (MM_A_STAGE_BYTES + b_boxes * MM_B_BOX_BYTES));
           if (p.tile32) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
               tma_load_tile32_2cta_hint(smem_a + stage * MM_A_STAGE_BYTES + j * (MM_A_STAGE_BYTES / 2), &tmap_a,
                                         leader_full, kb * 2 + j, m0 >> 5, pol_a);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 2 * b_boxes; ++i)
               tma_load_tile32_2cta_hint(smem_b + stage * MM2_B_STAGE_BYTES + i * (MM_B_BOX_BYTES / 2), &tmap_b,
                                         leader_full, (n0 >> 5) + i, kb * 2, pol_b);
           } else {
             tma_load_2d_2cta_hint(smem_a + stage * MM_A_STAGE_BYTES, &tmap_a, leader_full, kb * MM_BK, m0, pol_a);
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < b_boxes; ++i)
               tma_load_2d_2cta_hint(smem_b + stage * MM2_B_STAGE_BYTES + i * MM_B_BOX_BYTES, &tmap_b, leader_full,
                                     n0 + i * 64, kb * MM_BK, pol_b);
           }
@@ -504,7 +526,8 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++it) {
+      for (int work = pair; ok && work < p.num_work; work += num_pairs, ++it) {
+        const uint32_t idesc = work >= p.full_work ? p.idesc_half : p.idesc;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, ctx, 42);
@@ -523,7 +546,7 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
               const uint64_t a_desc = umma_smem_desc(a_addr + (k >> 1) * p.a_khalf + (k & 1) * (MM_UMMA_K * 2), 16,
                                                      p.a_sbo, p.swz);
               const uint64_t b_desc = umma_smem_desc(b_addr + k * p.b_kstep, p.b_lbo, p.b_sbo, p.swz);
-              umma_ss_2cta(d_tmem, a_desc, b_desc, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              umma_ss_2cta(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
             // release this ring slot in both CTAs once the MMAs above have read it
             const uint32_t e = smem_u32(&empty_bar[stage]);
@@ -548,11 +571,11 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
     int it = 0;
     int buf = 0;
     bool ok = true;
-    for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++it) {
-      int pid_m, pid_n;
-      tile_coords(p, tile, pid_m, pid_n);
-      const int m0 = pid_m * 256 + static_cast<int>(rank) * MM_BM;
-      const int n0 = pid_n * MM2_BN;
+    for (int work = pair; ok && work < p.num_work; work += num_pairs, ++it) {
+      const PairWork wk = pair_work(p, work);
+      const int m0 = wk.pid_m * 256 + static_cast<int>(rank) * MM_BM;
+      const int n0 = wk.col0;
+      const int chunks = wk.width / 64;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       ok = mbar_wait(&tmem_full_bar[acc], acc_phase, ctx, 44);
@@ -561,12 +584,12 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
       const int row = m0 + q * 32 + static_cast<int>(lane);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MM2_BN;
 #pragma unroll 1
-      for (int c = 0; c < MM2_BN / 64; ++c) {
+      for (int c = 0; c < chunks; ++c) {
         uint32_t v0[32], v1[32];
         tmem_ld_x32(t_row + c * 64, v0);
         tmem_ld_x32(t_row + c * 64 + 32, v1);
         tmem_wait_ld();
-        if (c == MM2_BN / 64 - 1) {
+        if (c == chunks - 1) {
           // this warp's part of the accumulator has left tensor memory: tell the leader's MMA thread
           tc_fence_before();
           __syncwarp();
@@ -657,6 +680,8 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   p.tile32 = a.tile32;
   p.n_extra = a.n_extra;
   p.idesc = umma_idesc_16bit_f32(MM_BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
+  p.idesc_half = p.idesc;   // the pair kernel's fields, unused here
+  p.num_work = p.full_work = p.num_tiles;
   p.status = status;
 
   // per device (function attributes belong to the current context), cheap enough to repeat
@@ -696,6 +721,7 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   p.tile32 = a.tile32;
   p.n_extra = a.n_extra;
   p.idesc = umma_idesc_16bit_f32(256, MM2_BN, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
+  p.idesc_half = umma_idesc_16bit_f32(256, MM2_BN / 2, /*a_mn_major=*/0, /*b_mn_major=*/1, a.dtype);
   p.l2_hint = 2;  // keep the group's A row panel in L2 (measured +2 % at 8192^3 over no hint; B evict_first loses)
   if (const char* h = getenv("B200K_MATMUL_L2_HINT")) p.l2_hint = atoi(h);
   p.status = status;
@@ -704,6 +730,15 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   const int max_pairs = dev->sm_count / 2;
   const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  // The last wave: if its tiles occupy at most half of the pairs, cut them in two so that it takes half as long
+  // (4096^3: 256 tiles on 74 pairs = 3 waves + 34 tiles -> 3 waves + 68 half tiles).
+  p.num_work = p.full_work = p.num_tiles;
+  const int rest = p.num_tiles % pairs;
+  const char* split_env = getenv("B200K_MATMUL_SPLIT_TAIL");
+  if (rest > 0 && 2 * rest <= pairs && !(split_env != nullptr && atoi(split_env) == 0)) {
+    p.full_work = p.num_tiles - rest;
+    p.num_work = p.full_work + 2 * rest;
+  }
   matmul_bf16_tcgen05_2cta_kernel<STAGES><<<2 * pairs, MM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, extra, p);
   count_launch();
   B200K_CHECK_LAUNCH("matmul_bf16_tcgen05_2cta_kernel");
