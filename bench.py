@@ -382,6 +382,16 @@ def secondary_workloads(torch, ops, gi, peaks, dist, world, rank, a, b, c, shard
     out["add_n2^26"] = {"ms": ms, "GB/s": 12 * n / ms / 1e6, "frac_of_hbm_peak": 12 * n / ms / 1e6 / hbm,
                         "l2": "inputs larger than L2, back-to-back launches", "ms_flushed_single": msf,
                         "GB/s_flushed_single": 12 * n / msf / 1e6}
+    # the reference's own size sweep of vector add (01-vector-add.py:119: n = 2^12 .. 2^27), extended to 2^28;
+    # back-to-back launches, so sizes that fit the 126 MB L2 (3 * 4 * n bytes) are served from it
+    sweep = {}
+    for kexp in range(12, 29, 2):
+        nk = 1 << kexp
+        xk, yk = torch.rand(nk, device="cuda"), torch.rand(nk, device="cuda")
+        msk = quick_ms(lambda: ops.add(xk, yk), torch, rep=20 if kexp < 26 else 8)
+        sweep[f"2^{kexp}"] = round(12 * nk / msk / 1e6, 1)
+        del xk, yk
+    out["add_sweep_GB/s"] = sweep
     xs = (xb * 8 - 4) * 3.14159265
     ms = quick_ms(lambda: ops.sin(xs), torch, rep=30)
     msf = flushed_ms(lambda: ops.sin(xs))
