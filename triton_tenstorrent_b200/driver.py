@@ -161,6 +161,9 @@ class B200Driver:
         torch.cuda.set_device(device)
 
     def get_current_stream(self, device_id=None):
+        raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+        if raw is not None:   # the handle without building a Stream object (this sits on every launch)
+            return raw(torch.cuda.current_device() if device_id is None else device_id)
         return torch.cuda.current_stream(device_id).cuda_stream
 
     def get_device_interface(self):

@@ -19,7 +19,14 @@ __all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", 
            "attention_with_lse", "device_status"]
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """Handle of the current CUDA stream of the current device (the raw query avoids building a Stream object on
+    every launch, which matters for the launch-bound sizes)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
