@@ -5,7 +5,7 @@
 // One CTA owns a pair of adjacent 128-row Q tiles of one (batch, head) (a single tile for HEAD_DIM 256,
 // where tensor memory and shared memory hold one) and walks the K/V blocks of 128 keys once for both:
 //   warps 0-3   softmax group of Q tile 0     warps 4-7   softmax group of Q tile 1
-//   warp 8      TMA producer (Q tiles, K/V ring of 32 KB slots in the order K0 V0 K1 V1 ...)
+//   warp 8      TMA producer (Q tiles, K/V ring of three 32 KB slots in the order K0 V0 K1 V1 ...)
 //   warp 9      tensor-memory owner and tcgen05.mma issuer
 //   warps 10-11 idle (they complete the third warpgroup so that it can release registers)
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  S = Q K^T is produced
@@ -41,7 +41,9 @@ constexpr int AT_BM = 128;            // rows per Q tile
 constexpr int AT_BN = 128;            // keys per K/V block
 constexpr int AT_THREADS = 384;         // three warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
 constexpr int AT_BOX_BYTES = 16384;   // one TMA box: 128 rows x 64 columns of bf16
-constexpr int AT_MAX_NSLOT = 5;       // K/V ring slots (2 for head dimension 256)
+constexpr int AT_MAX_NSLOT = 3;       // K/V ring slots (2 for head dimension 256).  Measured at D = 128, S = 4096:
+                                      // 3 slots 1269 / 1004 TFLOP/s (full / causal), 4: 1264 / 980, 5: 1253 / 970,
+                                      // 2: 1223 / 1004 -- a deeper prefetch only adds traffic ahead of its use
 constexpr int AT_NBAR = 2 + 2 + 2 * AT_MAX_NSLOT + 2 + 2 + 2;
 // Shared-memory layout for head dimension D: Q0 | Q1 | K/V ring | barriers.  A 128 x D tile is
 // max(D/64, 1) boxes of 128 rows x 128 bytes.  For D < 64 a row only fills its first 2*D bytes: TMA pads
