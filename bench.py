@@ -102,7 +102,9 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(power),
+        # nvidia-smi's readings lag the load by a sample or two, so the minimum and the mean are kept beside the median
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "sm_mhz_min": min(sm),
+                "sm_mhz_mean": round(statistics.fmean(sm), 1), "power_w_max": max(power),
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
