@@ -162,12 +162,30 @@ int b200k_attn_fwd_bf16(const void* q, const void* k, const void* v, void* o, fl
  *     with B200K_ERR_INVALID_ARG.  Other argument rules are those of b200k_attn_fwd_bf16.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress) with that
  *     device current; make that first call before any stream capture begins.
- *   - All calls on one device share the array.  Each call zeroes the status block on `stream` before the
- *     kernel; two calls whose kernels overlap on the GPU (different streams) race on it and on the row
- *     statistics, so serialise calls per device.
+ *   - All calls on one device share the array and it keeps the last call's contents: the row statistics are
+ *     write-only, the status word starts at zero (module load) and is only ever cleared by
+ *     b200k_attn_noalloc_status.  Two calls whose kernels overlap on the GPU (different streams) race on the
+ *     row statistics, so serialise calls per device.
+ *   - A bounded device-side wait that gives up on this path is recorded in the array, not in the word that
+ *     b200k_device_status reads (that function allocates on a device's first use): query it with
+ *     b200k_attn_noalloc_status.
  */
 int b200k_attn_fwd_bf16_noalloc(const void* q, const void* k, const void* v, void* o,
                                 int Z, int H, int N_CTX, int D, int causal, float sm_scale, void* stream);
+/*
+ * Status of the no-allocation attention path on the current device (no counterpart in the reference): copies
+ * the status word kept in the static array to *code on `stream`, synchronises the stream, and returns
+ * B200K_OK when it is zero, or B200K_ERR_DEVICE_TIMEOUT after clearing it when a bounded wait of an earlier
+ * b200k_attn_fwd_bf16_noalloc call gave up (that call's O is then incomplete).  Allocates nothing.
+ */
+int b200k_attn_noalloc_status(void* stream, uint32_t* code);
+/*
+ * b200k_selftest_wait_timeout reporting into the static array of the no-allocation path instead of the
+ * library's allocated status word (no counterpart in the reference): a one-warp kernel waits `budget_cycles`
+ * on a barrier nothing completes, gives up, records that and returns normally; b200k_attn_noalloc_status then
+ * reports B200K_ERR_DEVICE_TIMEOUT once.  Nothing faults or hangs.
+ */
+int b200k_attn_noalloc_selftest(int64_t budget_cycles, void* stream);
 /*
  * b200k_attn_fwd_bf16 whose epilogue stores every O tile to n_dests destinations o_dests[0..n_dests)
  * (1 <= n_dests <= 8, each a contiguous [Z,H,N_CTX,D] bf16 block, 16-byte aligned) instead of one; the

@@ -14,6 +14,7 @@ import torch
 
 ADD_SIZES = [1, 33, 1024, 5000, 98432]
 SIN_SIZES = [32, 1024, 98432]
+MUL_ADD_SIZES = [1, 1000, 4097, 98432]
 # (n, programs, row_count) of the row_count-loop add_kernel; the first is the tutorial's own launch
 # (n_cores = 130 > 97 rows, so 97 programs of one row each), the last leaves elements uncovered
 ADD_LOOP_CASES = [(98432, 97, 1), (50000, 7, 7), (33333, 3, 11), (50000, 5, 7)]
@@ -43,6 +44,15 @@ def _gen(seed: int) -> torch.Generator:
 def add_inputs(n: int, seed: int = 0):
     g = _gen(seed)
     return torch.rand(n, generator=g, dtype=torch.float32), torch.rand(n, generator=g, dtype=torch.float32)
+
+
+def mul_add_inputs(n: int, seed: int = 7):
+    """x, y ~ U[0,1) and z ~ U[-4pi, 4pi): products and sums that round (x*y is rounded before z is added)."""
+    g = _gen(seed)
+    x = torch.rand(n, generator=g, dtype=torch.float32)
+    y = torch.rand(n, generator=g, dtype=torch.float32)
+    z = (torch.rand(n, generator=g, dtype=torch.float32) * 8 - 4) * math.pi
+    return x, y, z
 
 
 def sin_inputs(n: int, seed: int = 0):

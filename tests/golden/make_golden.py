@@ -17,12 +17,12 @@ No reference file is modified or copied into this repository; only the resulting
 stored.
 
 Outputs (small .npz files, a few hundred KB in total):
-  add.npz, add_loop.npz, sin.npz, matmul.npz, matmul_fused.npz, attention.npz, matmul_tile32.npz
+  add.npz, add_loop.npz, mul_add.npz, sin.npz, matmul.npz, matmul_fused.npz, attention.npz, matmul_tile32.npz
 Inputs are regenerated from their seeds by `golden_inputs.py`; each .npz keeps a sha256 of the
 input bytes so that a drift of torch's CPU RNG cannot silently invalidate the vectors.
 
 Run:  REFERENCE_ROOT=<checkout of the reference> python tests/golden/make_golden.py [set ...]
-      (sets: add add_loop sin matmul matmul_fused attention matmul_tile32; default all)
+      (sets: add add_loop mul_add sin matmul matmul_fused attention matmul_tile32; default all)
 """
 from __future__ import annotations
 
@@ -51,6 +51,7 @@ KERNEL_SOURCES = {
     "ref_add": ("python/tutorials/01-vector-add.py", ["add_kernel"]),
     "ref_add_loop": ("python/tutorials/01-vector-add.loop.py", ["add_kernel"]),
     "ref_sin": ("examples/01-sin-kernel.py", ["sin_kernel"]),
+    "ref_muladd": ("python/tutorials/01-vector-mul-add.py", ["muladd_kernel"]),
     "ref_matmul": ("examples/matmul_tensor_descriptor/09-persistent-matmul.ttnn.py", ["matmul_kernel_tma"]),
     "ref_fused": ("python/tutorials/09-matmul-fused.py", ["matmul_kernel_fused"]),
     "ref_attn": ("examples/fused-attn/06-fused-attention.py", ["_attn_fwd_inner", "_maybe_make_tensor_desc", "_attn_fwd"]),
@@ -157,6 +158,16 @@ def main():
                 if n < 40000:
                     out[f"out_{tag}"] = o.numpy()
             np.savez_compressed(HERE / "add_loop.npz", **out)
+
+        if want("mul_add"):
+            # ---- muladd_kernel (python/tutorials/01-vector-mul-add.py:29-56), launched as muladd() does (:62-80)
+            out = {}
+            for n in gi.MUL_ADD_SIZES:
+                x, y, z = gi.mul_add_inputs(n)
+                o = torch.empty_like(x)
+                k["ref_muladd"].muladd_kernel[((n + 1023) // 1024,)](x, y, z, o, n, BLOCK_SIZE=1024)
+                out[f"in_sha_{n}"], out[f"out_{n}"] = np.array(gi.digest(x, y, z)), o.numpy()
+            np.savez_compressed(HERE / "mul_add.npz", **out)
 
         if want("sin"):
             # ---- sin_kernel (examples/01-sin-kernel.py:17-29)

@@ -116,6 +116,15 @@ def test_add_full_size_property():
     assert torch.equal(ops.add(x, y), x + y)
 
 
+@pytest.mark.parametrize("n", gi.MUL_ADD_SIZES)
+def test_mul_add_golden_bit_exact(golden_dir, n):
+    # golden vectors made by running the reference's muladd_kernel (python/tutorials/01-vector-mul-add.py:29-56)
+    g = np.load(golden_dir / "mul_add.npz")
+    x, y, z = gi.mul_add_inputs(n)
+    got = ops.mul_add(x.cuda(), y.cuda(), z.cuda()).cpu()
+    assert np.array_equal(got.numpy().view(np.uint32), g[f"out_{n}"].view(np.uint32))
+
+
 def test_mul_add_oracle_bit_exact():
     x, y = gi.add_inputs(98432, seed=7)
     z = gi.sin_inputs(98432, seed=8)
@@ -263,17 +272,21 @@ def test_matmul_fused_tail_bias():
     assert oracle.rel_frobenius(got.float(), oracle.golden_matmul(a, b, bias=bias_full, mode=2).float()) <= MATMUL_REL_FRO
 
 
-@pytest.mark.parametrize("S", [4096, 8192])
+@pytest.mark.parametrize("S", [4096, 8192, 16384])
 def test_matmul_full_size_rows_against_oracle(S):
-    # full-size problem on the GPU; the oracle recomputes a sample of rows (whole rows of C, all of B)
+    # full-size problem on the GPU (all three sizes of the workload definition); the oracle recomputes a sample of
+    # rows (whole rows of C, all of B)
     a, b = gi.matmul_inputs(S, S, S, seed=12)
-    got = ops.matmul_tma(a.cuda(), b.cuda())
-    rows = torch.tensor([0, 1, 127, 128, S // 2 + 3, S - 129, S - 1] + list(range(1000, 1000 + 25)))
+    ad, bd = a.cuda(), b.cuda()
+    got = ops.matmul_tma(ad, bd)
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, S // 2 + 3, S - 257, S - 129, S - 1] + list(range(1000, 1000 + 22)))
     ref = oracle.golden_matmul(a[rows], b)
     assert oracle.rel_frobenius(got[rows.cuda()].cpu().float(), ref.float()) <= MATMUL_REL_FRO
     # linearity in A: (2A).B == 2 (A.B) exactly (power-of-two scaling commutes with every rounding)
-    got2 = ops.matmul_tma((a * 2).cuda(), b.cuda())
-    assert torch.equal(got2, got * 2)
+    ad.mul_(2)
+    got2 = ops.matmul_tma(ad, bd)
+    got.mul_(2)
+    assert torch.equal(got2, got)
 
 
 def test_matmul_fused_workload_shape_sample():
@@ -557,11 +570,26 @@ def test_attention_full_size_heads_against_oracle(causal):
     Z, H, S, D = 4, 32, 4096, 128
     q, k, v = gi.attn_inputs(Z, H, S, D, seed=23)
     o, m = ops.attention_with_lse(q.cuda(), k.cuda(), v.cuda(), causal, D ** -0.5)
-    for (z, h) in ((0, 0), (3, 31)):
+    # the first head, one from the middle and the last one (the causal schedule merges the last heads' items)
+    for (z, h) in ((0, 0), (1, 17), (3, 31)):
         sl = (slice(z, z + 1), slice(h, h + 1))
         ref_o, ref_m = oracle.attention(q[sl], k[sl], v[sl], causal, D ** -0.5)
         assert float((o[sl].cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
         assert float((m[sl].cpu() - ref_m).abs().max()) <= 1e-4
+    # M of EVERY (batch, head) is the base-2 log-sum-exp of the scaled scores: recomputed head by head in fp32 on the GPU
+    # (an exact property of the workload, independent of the blockwise order)
+    scale = D ** -0.5
+    qd, kd = q.cuda(), k.cuda()
+    keep = torch.ones(S, S, dtype=torch.bool, device="cuda").tril() if causal else None
+    worst = 0.0
+    for z in range(Z):
+        for h in range(H):
+            sc = (qd[z, h].float() @ kd[z, h].float().t()) * scale
+            if causal:
+                sc = sc.masked_fill(~keep, float("-inf"))
+            lse2 = torch.logsumexp(sc, dim=-1) * 1.4426950408889634
+            worst = max(worst, float((m[z, h] - lse2).abs().max()))
+    assert worst <= 1e-3, f"M differs from logsumexp * log2(e) by {worst}"
     # rows of softmax sum to one: with V = 1 the output is exactly 1 (l normalisation)
     ones = torch.ones_like(v[:1, :2]).cuda()
     o1 = ops.attention(q[:1, :2].cuda(), k[:1, :2].cuda(), ones, causal, D ** -0.5)

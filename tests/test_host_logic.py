@@ -137,7 +137,7 @@ def test_attention_launch_surface(recording):
                             IS_HOPPER=False)
     call = recording[0]
     assert call["grid"] == (2, 6, 1)
-    assert call["function"] == "_attn_fwd:STAGE=3"
+    assert call["function"] == "_attn_fwd:STAGE=3,BLOCK_M=128"   # the grid is checked against BLOCK_M
     kinds = [k for k, _ in call["flat"]]
     assert kinds[0] == _lib.ARG_F32 and kinds[1] == _lib.ARG_PTR and len(kinds) == 4 + 40 + 1
     assert call["flat"][-1][1] == S

@@ -52,6 +52,17 @@ def test_add_loop_bit_exact(golden_dir, case):
     assert torch.equal(outb[:covered].view(torch.int16), (xb + yb)[:covered].view(torch.int16))
 
 
+@pytest.mark.parametrize("n", gi.MUL_ADD_SIZES)
+def test_mul_add_bit_exact(golden_dir, n):
+    # muladd_kernel (python/tutorials/01-vector-mul-add.py:29-56): x * y rounded, then + z rounded
+    g = np.load(golden_dir / "mul_add.npz")
+    x, y, z = gi.mul_add_inputs(n)
+    assert str(g[f"in_sha_{n}"]) == gi.digest(x, y, z), "input generator drifted from the golden vectors"
+    for workers in (1, 3, 0):
+        out = oracle.mul_add(x, y, z, block=1024, workers=workers)
+        assert np.array_equal(out.numpy().view(np.uint32), g[f"out_{n}"].view(np.uint32))
+
+
 @pytest.mark.parametrize("n", gi.SIN_SIZES)
 def test_sin_within_2ulp(golden_dir, n):
     g = np.load(golden_dir / "sin.npz")

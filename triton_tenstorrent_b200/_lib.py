@@ -81,6 +81,8 @@ SIGNATURES = {
                                     c_int, c_float, c_void_p]),
     "b200k_attn_fwd_bf16_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                             c_float, c_void_p]),
+    "b200k_attn_noalloc_status": (c_int, [c_void_p, POINTER(c_uint32)]),
+    "b200k_attn_noalloc_selftest": (c_int, [c_int64, c_void_p]),
     "b200k_attn_fwd_bf16_multi": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int, c_void_p, c_int, c_int,
                                           c_int, c_int, c_int, c_float, c_void_p]),
     "b200k_attn_causal_schedule": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int), c_int, POINTER(c_int)]),

@@ -44,7 +44,7 @@ constexpr int AT_BOX_BYTES = 16384;   // one TMA box: 128 rows x 64 columns of b
 constexpr int AT_MAX_NSLOT = 3;       // K/V ring slots (2 for head dimension 256).  Measured at D = 128, S = 4096:
                                       // 3 slots 1269 / 1004 TFLOP/s (full / causal), 4: 1264 / 980, 5: 1253 / 970,
                                       // 2: 1223 / 1004 -- a deeper prefetch only adds traffic ahead of its use
-constexpr int AT_NBAR = 2 + 2 + 2 * AT_MAX_NSLOT + 2 + 2 + 2;
+constexpr int AT_NBAR = 2 + 2 + 2 * AT_MAX_NSLOT + 2 + 2 + 2 + 2;
 // Shared-memory layout for head dimension D: Q0 | Q1 | K/V ring | barriers.  A 128 x D tile is
 // max(D/64, 1) boxes of 128 rows x 128 bytes.  For D < 64 a row only fills its first 2*D bytes: TMA pads
 // every box row to the 128-byte swizzle span, the MMAs and the TMA store touch only the filled part.
@@ -68,6 +68,22 @@ struct AttnCfg {
 };
 
 constexpr float AT_RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+// Two refinements of the softmax path, both measured at Z=4, H=32, N_CTX=4096 (non-causal TFLOP/s at HEAD_DIM 128 / 64;
+// with neither: 1261 / 683):
+//   halves       P reaches the MMA issuer in two halves of 64 keys, so that half of the PV product runs while the last
+//                exponentials are computed and only 4 + 8 MMAs stand between the end of a block's softmax and the next
+//                block's scores: 1293-1324 / 766-771.  Always on (B200K_ATTN_P_HALVES=0 builds the whole-block form).
+//   early start  the first 32 exponentials start with the current exponent base while the row maximum is still being
+//                computed, and are redone from tensor memory when the base has to move: 1287 / 747 alone, 1255 / 795
+//                together with the halves.  On for HEAD_DIM <= 64 only, where the exponentials are the bound.
+// Tried and dropped: handing P over as 64 + 32 + 32 keys (-10 %: the extra hand-off costs the softmax warps more than
+// the two MMAs it moves), and interleaving the scale / sum / pack instructions by hand between the ex2 instructions
+// (one warp's mix of 2-3 other instructions per ex2 runs at 9-12 cycles per ex2 however it is ordered; measured with
+// a microbenchmark and in the kernel).
+#ifndef B200K_ATTN_P_HALVES
+#define B200K_ATTN_P_HALVES 1
+#endif
 
 struct AttnParams {
   int ZH, N_CTX;
@@ -155,6 +171,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
   using Cfg = AttnCfg<D>;
   constexpr int AT_TILE_BYTES = Cfg::TILE_BYTES;
   constexpr int AT_NSLOT = Cfg::NSLOT;
+  constexpr bool EARLY_START = D <= 64;   // see the note on the softmax refinements above
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -167,7 +184,8 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
   uint64_t* s_full = kv_empty + AT_MAX_NSLOT;
   uint64_t* p_full = s_full + 2;
   uint64_t* o_full = p_full + 2;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(o_full + 2);
+  uint64_t* p_half = o_full + 2;    // first 64 keys of P are in tensor memory
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(p_half + 2);
   uint32_t* abort_smem = tmem_ptr_smem + 1;
 
   const int warp_idx = threadIdx.x >> 5;
@@ -180,6 +198,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       mbar_init(&q_empty[t], 4);
       mbar_init(&s_full[t], 1);
       mbar_init(&p_full[t], 4);
+      mbar_init(&p_half[t], 4);
       mbar_init(&o_full[t], 1);
     }
     for (int s = 0; s < AT_NSLOT; ++s) {
@@ -277,12 +296,13 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       }
       __syncwarp();
     };
-    auto issue_pv = [&](int t, int slot_idx, bool accumulate) {
-      // O_t (+)= P_t V : 8 MMAs of K = 16 over the keys; P_t is bf16 in TMEM (8 columns per K step)
+    auto issue_pv = [&](int t, int slot_idx, bool accumulate, int k0, int k1) {
+      // O_t (+)= P_t V for the key steps [k0, k1) of the block's 8 (K = 16 keys each); P_t is bf16 in TMEM
+      // (8 columns per step)
       if (lane == 0) {
         const uint64_t vd = v_desc0 + static_cast<uint64_t>((slot_idx * AT_TILE_BYTES) >> 4);
 #pragma unroll
-        for (int k = 0; k < AT_BN / 16; ++k)
+        for (int k = k0; k < k1; ++k)
           umma_ts(tmem_base + Cfg::O_COL0 + t * 128, tmem_base + t * 128 + k * 8, vd + static_cast<uint64_t>((k * 2048) >> 4),
                   IDESC_PV, (accumulate || k > 0) ? 1u : 0u);
       }
@@ -319,11 +339,18 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         bool next_k_ready = false;
         for (int t = 0; ok && t < 2; ++t) {
           if (j < it.nblk[t]) {
+#if B200K_ATTN_P_HALVES
+            // the first 64 keys of P arrive while the softmax group still works on the other 64
+            ok = mbar_wait(&p_half[t], p_cnt[t] & 1u, ctx, 26);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, v_slot, j > 0, 0, AT_BN / 32);
+#endif
             ok = mbar_wait(&p_full[t], p_cnt[t] & 1u, ctx, 23);
             if (!ok) break;
             ++p_cnt[t];
             tc_fence_after();
-            issue_pv(t, v_slot, j > 0);
+            issue_pv(t, v_slot, j > 0, B200K_ATTN_P_HALVES ? AT_BN / 32 : 0, AT_BN / 16);
             if (j == it.nblk[t] - 1) {
               if (lane == 0) umma_commit(&o_full[t]);
               __syncwarp();
@@ -400,13 +427,47 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
             if (c + 96 > r) s3[c] = ninf;
           }
         }
+        const bool diag = p.causal && j == n_me - 1;
+        const uint64_t scale2 = pack_f32x2(scale, scale);
+        uint64_t negm2 = pack_f32x2(-m_used, -m_used);
+        uint64_t sum_a = 0, sum_b = 0;  // bit pattern of (0.f, 0.f)
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        if constexpr (EARLY_START) {
+        // The exponent base m_used only moves when a row maximum outgrows it by 2^8, which after the first block
+        // of an item is rare.  So the first 32 exponentials are started with the current base while the row maximum
+        // over the other 96 scores is still being computed (the max instructions fill the issue slots the ex2 unit
+        // leaves free); if the vote below then finds that the base must move, those 32 are recomputed from the
+        // scores still in tensor memory.  The first block of an item (m_used = -inf) always takes that path.
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) mx0 = fmax3(mx0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1])), scale2, negm2), x0, x1);
+          s0[2 * c] = __float_as_uint(x0);
+          s0[2 * c + 1] = __float_as_uint(x1);
+        }
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          s0[c] = __float_as_uint(ex2_approx(__uint_as_float(s0[c])));
+          s0[c + 1] = __float_as_uint(ex2_approx(__uint_as_float(s0[c + 1])));
+          mx1 = fmax3(mx1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+          mx2 = fmax3(mx2, __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
+          mx3 = fmax3(mx3, __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
+        }
+#pragma unroll
+        for (int c = 0; c < 16; c += 2) {
+          sum_a = add_f32x2(sum_a, pack_f32x2(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1])));
+          sum_b = add_f32x2(sum_b, pack_f32x2(__uint_as_float(s0[2 * c + 2]), __uint_as_float(s0[2 * c + 3])));
+        }
+        } else {
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {  // 3-input max: two new scores per instruction
           mx0 = fmax3(mx0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
           mx1 = fmax3(mx1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
           mx2 = fmax3(mx2, __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
           mx3 = fmax3(mx3, __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
+        }
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const float m_new = fmaxf(m_used, mx * scale);
@@ -436,15 +497,26 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
               tmem_st_x16(t_o, o);
             }
           }
+          negm2 = pack_f32x2(-m_used, -m_used);
+          if constexpr (EARLY_START) {
+          // redo the first 32 exponentials with the new base: their scores are still in tensor memory
+          tmem_ld_x32(t_s + 0, s0);
+          tmem_wait_ld();
+          if (diag) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              if (c > r) s0[c] = 0xFF800000u;
+          }
+          sum_a = 0;
+          sum_b = 0;
+          exp_block32(s0, scale2, negm2, sum_a, sum_b);
+          }
         }
         // p = exp2(s * scale - m): the multiply-subtract and the row sum run two lanes per instruction
         // (fma.rn.f32x2 / add.rn.f32x2); each lane rounds exactly like the scalar fma / add.
-        const uint64_t scale2 = pack_f32x2(scale, scale);
-        const uint64_t negm2 = pack_f32x2(-m_used, -m_used);
-        uint64_t sum_a = 0, sum_b = 0;  // bit pattern of (0.f, 0.f)
         // Three passes per 32 scores, each over independent registers, so that the latency of the
         // special-function unit is covered by the other exponentials instead of by stalls.
-        exp_block32(s0, scale2, negm2, sum_a, sum_b);
+        if constexpr (!EARLY_START) exp_block32(s0, scale2, negm2, sum_a, sum_b);
         exp_block32(s1, scale2, negm2, sum_a, sum_b);
         {
           uint32_t pk[32];
@@ -456,6 +528,14 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           tmem_st_x32(t_s, pk);
         }
         exp_block32(s2, scale2, negm2, sum_a, sum_b);
+#if B200K_ATTN_P_HALVES
+        // the first 64 keys of P have had the time of 32 exponentials to land in tensor memory: hand them over, so
+        // that half of the PV product runs while the last 32 exponentials are computed
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_half[t]);
+#endif
         exp_block32(s3, scale2, negm2, sum_a, sum_b);
         {
           uint32_t pk[32];
@@ -581,8 +661,9 @@ static int attn_check_args(const AttnArgs& a) {
   for (int d = 0; d < a.n_extra; ++d)
     if (a.extra_o[d] == nullptr || (reinterpret_cast<uintptr_t>(a.extra_o[d]) & 15u))
       return set_error(B200K_ERR_INVALID_ARG, "attention: extra destination %d is null or not 16-byte aligned", d);
-  const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
-  if (rows > 0x7FFFFFFF) return set_error(B200K_ERR_INVALID_ARG, "attention: Z*H*N_CTX exceeds 2^31-1 rows");
+  // Z*H first (two positive ints cannot overflow 64 bits), then the row count
+  const int64_t zh = static_cast<int64_t>(a.Z) * a.H;
+  if (zh > 0x7FFFFFFF || zh * a.N_CTX > 0x7FFFFFFF) return set_error(B200K_ERR_INVALID_ARG, "attention: Z*H*N_CTX exceeds 2^31-1 rows");
   if (!(a.sm_scale > 0.f) || !isfinite(a.sm_scale)) return set_error(B200K_ERR_INVALID_ARG, "attention: sm_scale must be positive and finite");
   return B200K_OK;
 }
@@ -645,15 +726,41 @@ std::vector<int> attn_schedule(int ZH, int num_pairs, int num_mblk, int ntile, i
   return table;
 }
 
-static int get_schedule(const SchedKey& key, const int** dev_table, int* rounds) {
+// At most this many schedule tables are kept per process; a caller that walks through more shapes than that gets
+// the tables rebuilt (after a device synchronisation, so that no launch in flight still reads a freed one).
+constexpr size_t AT_MAX_SCHEDULES = 64;
+
+static int get_schedule(const SchedKey& key, cudaStream_t stream, const int** dev_table, int* rounds) {
   std::lock_guard<std::mutex> lock(g_sched_mutex);
   auto it = g_sched.find(key);
   if (it == g_sched.end()) {
+    if (g_sched.size() >= AT_MAX_SCHEDULES) {
+      B200K_CHECK_CUDA(cudaDeviceSynchronize());
+      for (auto& kv : g_sched) {
+        int cur = 0;
+        if (cudaGetDevice(&cur) == cudaSuccess && cur == kv.first.device) {
+          cudaFree(kv.second.dev);
+        } else if (cudaSetDevice(kv.first.device) == cudaSuccess) {
+          cudaDeviceSynchronize();
+          cudaFree(kv.second.dev);
+          cudaSetDevice(cur);
+        }
+      }
+      g_sched.clear();
+    }
     int r = 0;
     const std::vector<int> table = attn_schedule(key.ZH, key.num_pairs, key.num_mblk, key.ntile, key.grid, &r);
     int* dev = nullptr;
     B200K_CHECK_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), table.size() * sizeof(int)));
-    B200K_CHECK_CUDA(cudaMemcpy(dev, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice));
+    // Upload on the launch stream and wait for it: a copy from pageable memory on the legacy stream is not ordered
+    // with a non-blocking stream, so the first launch of a shape on a side stream could otherwise read the table
+    // before it has arrived.  First use of a shape only.
+    cudaError_t e = cudaMemcpyAsync(dev, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) {
+      cudaFree(dev);
+      return set_error(B200K_ERR_CUDA, "attention: uploading the causal schedule failed: %s", cudaGetErrorString(e));
+    }
     it = g_sched.emplace(key, SchedTable{dev, r}).first;
   }
   *dev_table = it->second.dev;
@@ -699,7 +806,7 @@ static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uin
     grid = p.num_items < sm_count ? p.num_items : sm_count;   // the table balances any grid: use every SM
     int dev = 0;
     B200K_CHECK_CUDA(cudaGetDevice(&dev));
-    if ((rc = get_schedule(SchedKey{dev, p.ZH, p.num_pairs, p.num_mblk, p.ntile, grid}, &p.sched, &p.rounds)) != 0) return rc;
+    if ((rc = get_schedule(SchedKey{dev, p.ZH, p.num_pairs, p.num_mblk, p.ntile, grid}, stream, &p.sched, &p.rounds)) != 0) return rc;
   }
   // function attributes belong to the current context (per device); cheap enough to repeat
 #define B200K_ATTN_LAUNCH(DD)                                                                                     \
@@ -762,32 +869,32 @@ static std::mutex g_noalloc_mutex;
 
 // Per-device set-up (first call on a device, with that device current): the array's name is only a
 // host-side handle, so its device address is looked up once and cached.  Nothing is allocated.
-static const NoAllocDevice* noalloc_device() {
+// Returns B200K_OK and the device record, or the status code that matches the error message.
+static int noalloc_device(const NoAllocDevice** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= 64) {
-    set_error(B200K_ERR_NO_DEVICE, "attention (no-alloc): no usable current device (%s)", cudaGetErrorString(e));
-    return nullptr;
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return set_error(B200K_ERR_NO_DEVICE, "attention (no-alloc): no usable current device (%s)", cudaGetErrorString(e));
+  if (!g_noalloc_ready[dev].load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ready[dev].load(std::memory_order_acquire)) {
+      NoAllocDevice d{};
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_attn_noalloc_scratch);
+      if (e != cudaSuccess || ptr == nullptr)
+        return set_error(B200K_ERR_CUDA, "attention (no-alloc): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      d.scratch = static_cast<uint32_t*>(ptr);
+      if ((e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+          (e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+        return set_error(B200K_ERR_CUDA, "attention (no-alloc): cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
+      g_noalloc_dev[dev] = d;
+      g_noalloc_ready[dev].store(1, std::memory_order_release);
+    }
   }
-  if (g_noalloc_ready[dev].load(std::memory_order_acquire)) return &g_noalloc_dev[dev];
-  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
-  if (g_noalloc_ready[dev].load(std::memory_order_acquire)) return &g_noalloc_dev[dev];
-  NoAllocDevice d{};
-  void* ptr = nullptr;
-  e = cudaGetSymbolAddress(&ptr, g_attn_noalloc_scratch);
-  if (e != cudaSuccess || ptr == nullptr) {
-    set_error(B200K_ERR_CUDA, "attention (no-alloc): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-    return nullptr;
-  }
-  d.scratch = static_cast<uint32_t*>(ptr);
-  if ((e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
-      (e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) {
-    set_error(B200K_ERR_CUDA, "attention (no-alloc): cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
-    return nullptr;
-  }
-  g_noalloc_dev[dev] = d;
-  g_noalloc_ready[dev].store(1, std::memory_order_release);
-  return &g_noalloc_dev[dev];
+  if (g_noalloc_dev[dev].cc_major != 10)
+    return set_error(B200K_ERR_NO_DEVICE, "attention (no-alloc): needs an sm_100 device");
+  *out = &g_noalloc_dev[dev];
+  return B200K_OK;
 }
 
 }  // namespace b200k
@@ -796,24 +903,58 @@ extern "C" int b200k_attn_fwd_bf16_noalloc(const void* q, const void* k, const v
                                            int D, int causal, float sm_scale, void* stream) {
   using namespace b200k;
   clear_error();
-  const int64_t rows = static_cast<int64_t>(Z) * H * N_CTX;
-  if (Z > 0 && H > 0 && N_CTX > 0 && rows > B200K_ATTN_NOALLOC_MAX_ROWS)
-    return set_error(B200K_ERR_INVALID_ARG,
-                     "attention (no-alloc): Z*H*N_CTX = %lld query rows exceed the %d rows the static scratch holds; "
-                     "split the batch or use b200k_attn_fwd_bf16 with a caller-provided M buffer",
-                     (long long)rows, B200K_ATTN_NOALLOC_MAX_ROWS);
+  if (Z > 0 && H > 0 && N_CTX > 0) {
+    // Z*H first: the product of two positive ints fits 64 bits, and once it is within the limit so does the row count
+    const int64_t zh = static_cast<int64_t>(Z) * H;
+    if (zh > B200K_ATTN_NOALLOC_MAX_ROWS || zh * N_CTX > B200K_ATTN_NOALLOC_MAX_ROWS)
+      return set_error(B200K_ERR_INVALID_ARG,
+                       "attention (no-alloc): Z*H*N_CTX = %d*%d*%d query rows exceed the %d rows the static scratch holds; "
+                       "split the batch or use b200k_attn_fwd_bf16 with a caller-provided M buffer",
+                       Z, H, N_CTX, B200K_ATTN_NOALLOC_MAX_ROWS);
+  }
   // dummy non-null M so that the shared checks apply unchanged; replaced below
   AttnArgs a{q, k, v, o, reinterpret_cast<float*>(uintptr_t(16)), Z, H, N_CTX, D, causal, sm_scale};
-  const int rc = attn_check_args(a);
+  int rc = attn_check_args(a);
   if (rc != B200K_OK) return rc;
-  const NoAllocDevice* dev = noalloc_device();
-  if (dev == nullptr) return B200K_ERR_NO_DEVICE;
-  if (dev->cc_major != 10) return set_error(B200K_ERR_NO_DEVICE, "attention (no-alloc): needs an sm_100 device");
+  const NoAllocDevice* dev = nullptr;
+  if ((rc = noalloc_device(&dev)) != B200K_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // the status block must start at zero (the kernel records only the first failure); the row
-  // statistics are write-only and need no clearing
-  B200K_CHECK_CUDA(cudaMemsetAsync(dev->scratch, 0, 64 * sizeof(uint32_t), s));
+  // A failure that an earlier call recorded stays in word 0 until b200k_attn_noalloc_status has reported it (the
+  // kernel records only into a zero word), so nothing is cleared here; the row statistics are write-only.
   a.lse2 = reinterpret_cast<float*>(dev->scratch + 64);
   return attn_launch(a, s, dev->sm_count, dev->scratch, /*may_allocate=*/false);  // strided items, no schedule table
 }
 
+// The status word of the no-allocation path lives in the static array (word 0), where b200k_device_status, which
+// reads the library's allocated per-device word, never looks.  This reader copies it to the caller's host word on
+// `stream`, waits for the stream, and clears it after reporting a failure.  It allocates nothing either.
+extern "C" int b200k_attn_noalloc_status(void* stream, uint32_t* code) {
+  using namespace b200k;
+  clear_error();
+  const NoAllocDevice* dev = nullptr;
+  const int rc = noalloc_device(&dev);
+  if (rc != B200K_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t host = 0;
+  B200K_CHECK_CUDA(cudaMemcpyAsync(&host, dev->scratch, sizeof(host), cudaMemcpyDeviceToHost, s));
+  B200K_CHECK_CUDA(cudaStreamSynchronize(s));
+  if (code != nullptr) *code = host;
+  if (host != 0) {
+    B200K_CHECK_CUDA(cudaMemsetAsync(dev->scratch, 0, 2 * sizeof(uint32_t), s));
+    B200K_CHECK_CUDA(cudaStreamSynchronize(s));
+    return set_error(B200K_ERR_DEVICE_TIMEOUT, "a bounded device-side wait of the no-allocation attention gave up (site %u)", host >> 8);
+  }
+  return B200K_OK;
+}
+
+// The bounded-wait self-test (a wait on a barrier that nothing completes, with a small cycle budget) reporting into the
+// static array's status block instead of the allocated per-device word: shows that a wait which gives up on the
+// no-allocation path is visible through b200k_attn_noalloc_status.  Faults nothing; the kernel returns normally.
+extern "C" int b200k_attn_noalloc_selftest(int64_t budget_cycles, void* stream) {
+  using namespace b200k;
+  clear_error();
+  const NoAllocDevice* dev = nullptr;
+  const int rc = noalloc_device(&dev);
+  if (rc != B200K_OK) return rc;
+  return selftest_wait_timeout_at(dev->scratch, budget_cycles, static_cast<cudaStream_t>(stream));
+}

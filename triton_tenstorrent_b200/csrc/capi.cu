@@ -67,6 +67,8 @@ const DeviceInfo* current_device_info() {
   d.max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
   e = cudaMalloc(reinterpret_cast<void**>(&d.status_word), 8 * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(d.status_word, 0, 8 * sizeof(uint32_t));
+  // the memset runs on the legacy stream, which non-blocking streams are not ordered with: wait for it (first use only)
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     set_error(B200K_ERR_CUDA, "status word allocation: %s", cudaGetErrorString(e));
     return nullptr;
@@ -273,6 +275,7 @@ static int generic_launch(const char* kernel_name, int gx, int gy, int gz, cudaS
     spec = spec_str.c_str();
   }
   ArgCursor c{args, nargs};
+  if (name == "muladd_kernel") name = "mul_add_kernel";   // the spelling of python/tutorials/01-vector-mul-add.py:29
   if (name == "add_kernel" || name == "sin_kernel" || name == "mul_add_kernel") {
     if (gy != 1 || gz != 1) return set_error(B200K_ERR_INVALID_ARG, "launch %s: 1-D grid expected", name.c_str());
     const int nptr = name == "add_kernel" ? 3 : (name == "sin_kernel" ? 2 : 4);
@@ -377,6 +380,9 @@ static int generic_launch(const char* kernel_name, int gx, int gy, int gz, cudaS
       if (d->shape[0] != y || d->shape[1] != D || d->strides[0] != D || d->strides[1] != 1)
         return set_error(B200K_ERR_INVALID_ARG, "launch _attn_fwd: descriptors must be contiguous [Z*H*N_CTX, HEAD_DIM]");
     if (gy != Z * H || gz != 1) return set_error(B200K_ERR_INVALID_ARG, "launch _attn_fwd: grid must be (cdiv(N_CTX,BLOCK_M), Z*H, 1)");
+    const long block_m = spec_value(spec, "BLOCK_M", 0);
+    if (block_m > 0 && gx != (n_ctx + block_m - 1) / block_m)
+      return set_error(B200K_ERR_INVALID_ARG, "launch _attn_fwd: grid x = %d, expected cdiv(N_CTX=%lld, BLOCK_M=%ld)", gx, (long long)n_ctx, block_m);
     const long stage = spec_value(spec, "STAGE", 1);
     if (stage != 1 && stage != 3) return set_error(B200K_ERR_INVALID_ARG, "launch _attn_fwd: STAGE must be 1 or 3");
     AttnArgs aa{q.base, k.base, v.base, o.base, lse, (int)Z, (int)H, (int)n_ctx, (int)D, stage == 3 ? 1 : 0, sm_scale};

@@ -109,5 +109,7 @@ int attn_supported(int D, int N_CTX);
 // returns the table [rounds][grid] of item numbers (-1 = none).  Pure host code.
 std::vector<int> attn_schedule(int ZH, int num_pairs, int num_mblk, int ntile, int grid, int* rounds_out);
 int selftest_wait_timeout(long long budget_cycles, cudaStream_t s);
+// The same self-test reporting into `status_words` (device memory, at least two words: status, kernel's own outcome).
+int selftest_wait_timeout_at(uint32_t* status_words, long long budget_cycles, cudaStream_t s);
 
 }  // namespace b200k

@@ -53,6 +53,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test with a suspend-time hint: the thread may be parked by the hardware for up to `ns` nanoseconds (it is
+// woken when the phase completes), so a waiting warp does not compete for issue slots with the working warps of its
+// scheduler.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
+#ifndef B200K_WAIT_PARK_NS
+#define B200K_WAIT_PARK_NS 0
+#endif
+
 // Cycle budget of one bounded wait (~1 s at 2 GHz).  A healthy pipeline never comes close.
 #ifndef B200K_WAIT_CYCLES
 #define B200K_WAIT_CYCLES (2000000000ll)
@@ -73,7 +94,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
+#if B200K_WAIT_PARK_NS > 0
+    if (mbar_try_wait_parked(bar, parity, B200K_WAIT_PARK_NS)) return true;
+    spins |= 63u;
+#else
     if (mbar_try_wait(bar, parity)) return true;
+#endif
     if ((++spins & 63u) == 0) {
       if (*ctx.abort_flag != 0) return false;
       if (clock64() - t0 > ctx.budget) {

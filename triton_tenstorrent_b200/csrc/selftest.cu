@@ -23,16 +23,22 @@ __global__ void __launch_bounds__(32) selftest_wait_timeout_kernel(uint32_t* sta
   if (threadIdx.x == 0) *returned_flag = ok ? 1u : 2u;   // 2: the wait gave up and the kernel carried on
 }
 
+int selftest_wait_timeout_at(uint32_t* status_words, long long budget_cycles, cudaStream_t stream) {
+  if (budget_cycles <= 0 || budget_cycles > 4000000000ll)
+    return set_error(B200K_ERR_INVALID_ARG, "selftest: budget must be in (0, 4e9] cycles");
+  // word 0 is the status word; word 1 receives the kernel's own view of the outcome
+  selftest_wait_timeout_kernel<<<1, 32, 0, stream>>>(status_words, budget_cycles, status_words + 1);
+  count_launch();
+  B200K_CHECK_LAUNCH("selftest_wait_timeout_kernel");
+  return B200K_OK;
+}
+
 int selftest_wait_timeout(long long budget_cycles, cudaStream_t stream) {
   if (budget_cycles <= 0 || budget_cycles > 4000000000ll)
     return set_error(B200K_ERR_INVALID_ARG, "selftest: budget must be in (0, 4e9] cycles");
   const DeviceInfo* dev = current_device_info();
   if (dev == nullptr) return B200K_ERR_NO_DEVICE;
-  // word 0 is the status word; word 1 receives the kernel's own view of the outcome
-  selftest_wait_timeout_kernel<<<1, 32, 0, stream>>>(dev->status_word, budget_cycles, dev->status_word + 1);
-  count_launch();
-  B200K_CHECK_LAUNCH("selftest_wait_timeout_kernel");
-  return B200K_OK;
+  return selftest_wait_timeout_at(dev->status_word, budget_cycles, stream);
 }
 
 }  // namespace b200k

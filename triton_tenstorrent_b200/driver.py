@@ -28,7 +28,7 @@ from .tensor_descriptor import TensorDescriptor
 GPUTarget = namedtuple("GPUTarget", ["backend", "arch", "warp_size"])
 
 # kernels this library implements (the reference's compiled-kernel names)
-KERNEL_NAMES = ("add_kernel", "sin_kernel", "mul_add_kernel", "matmul_kernel_tma", "matmul_kernel_fused", "matmul_kernel",
+KERNEL_NAMES = ("add_kernel", "sin_kernel", "mul_add_kernel", "muladd_kernel", "matmul_kernel_tma", "matmul_kernel_fused", "matmul_kernel",
                 "_attn_fwd")
 
 
@@ -57,11 +57,12 @@ def flatten_args(signature: dict, args) -> list:
             continue
         if isinstance(arg, torch.Tensor):
             flat.append((_lib.ARG_PTR, arg.data_ptr()))
-        elif isinstance(arg, TensorDescriptor):
+        elif isinstance(arg, TensorDescriptor) or (hasattr(arg, "base") and hasattr(arg, "strides") and hasattr(arg, "block_shape")):
+            # this package's descriptor, or any object of the same shape (Triton's own TensorDescriptor)
             dims = [(_lib.ARG_I64, int(d)) for d in arg.shape] + [(_lib.ARG_I64, int(s)) for s in arg.strides]
             flat.append((_lib.ARG_PTR, arg.base.data_ptr()))
             flat.extend(dims)
-            flat.append((_lib.ARG_I32, 1 if arg.padding == "nan" else 0))
+            flat.append((_lib.ARG_I32, 1 if getattr(arg, "padding", "zero") == "nan" else 0))
             flat.extend(dims)  # shape and strides a second time, as the reference passes them
         elif isinstance(arg, bool):
             flat.append((_lib.ARG_I32, int(arg)))

@@ -173,5 +173,5 @@ _attn_fwd = Kernel(
      "FP8_OUTPUT", "STAGE", "warp_specialize", "IS_HOPPER"],
     ["fp32", "*fp32", "i32", "i32", "tensordesc", "tensordesc", "tensordesc", "tensordesc", "i32"] + ["constexpr"] * 7,
     {"BLOCK_M": 128, "BLOCK_N": 128, "FP8_OUTPUT": False, "STAGE": 1, "warp_specialize": True, "IS_HOPPER": False},
-    spec_keys=("STAGE",))
+    spec_keys=("STAGE", "BLOCK_M"))
 _attn_fwd_jit = _attn_fwd.fn

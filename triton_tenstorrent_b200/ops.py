@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_multi", "matmul_fused", "matmul_tma_fused", "attention", "attention_multi",
+__all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_tma_host_rows", "matmul_multi", "matmul_fused", "matmul_tma_fused", "attention", "attention_multi",
            "attention_with_lse", "device_status"]
 
 
@@ -168,7 +168,19 @@ def _side_streams(device):
     return _copy_streams[key]
 
 
-def _matmul_host_streamed(a, b, out, bias, bias_kind, act, round_before_bias):
+def matmul_tma_host_rows(a: torch.Tensor, b_dev: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """C = A.B for a HOST A (and host result) against a B that is already resident on the current device:
+    the row-block pipeline of matmul_tma's host path without the upload of B.  Used when B reaches the
+    GPU some other way, e.g. gathered over NVLink from the other GPUs of the box."""
+    if a.is_cuda or not b_dev.is_cuda:
+        raise ValueError("matmul_tma_host_rows: a must be a host tensor and b_dev a CUDA tensor")
+    if a.shape[0] < 2 * _HOST_CHUNK_ROWS:
+        c = _matmul_call(a, b_dev)
+        return _like_input(c, a, out)
+    return _matmul_host_streamed(a, None, out, None, _lib.BIAS_NONE, _lib.ACT_NONE, 0, b_dev=b_dev)
+
+
+def _matmul_host_streamed(a, b, out, bias, bias_kind, act, round_before_bias, b_dev=None):
     """C = epilogue(A.B) for HOST operands, as a three-stage pipeline over row blocks of A and C:
     while block i is multiplied, block i+1 of A travels to the device and block i-1 of C travels back
     (PCIe is full duplex), so a call costs about the upload of B plus the upload of A instead of the
@@ -177,7 +189,7 @@ def _matmul_host_streamed(a, b, out, bias, bias_kind, act, round_before_bias):
     _require_cuda()
     device = torch.device("cuda", torch.cuda.current_device())
     M, K = a.shape
-    N = b.shape[1]
+    N = b.shape[1] if b_dev is None else b_dev.shape[1]
     main = torch.cuda.current_stream(device)
     s_in, s_out = _side_streams(device)
     if out is None:
@@ -189,7 +201,8 @@ def _matmul_host_streamed(a, b, out, bias, bias_kind, act, round_before_bias):
     s_in.wait_stream(main)
     s_out.wait_stream(main)
     with torch.cuda.stream(s_in):
-        b_dev = b.to(device, non_blocking=True)
+        if b_dev is None:      # otherwise B is already on the device (ordered on the main stream)
+            b_dev = b.to(device, non_blocking=True)
         bias_dev = bias.to(device, non_blocking=True) if bias is not None else None
     blocks = [(r, min(r + _HOST_CHUNK_ROWS, M)) for r in range(0, M, _HOST_CHUNK_ROWS)]
     for (r0, r1) in blocks:

@@ -140,3 +140,38 @@ def attention_all_gather(q_shard, k_shard, v_shard, causal, sm_scale, gathered: 
                         remote_ptrs=gathered.remote_blocks())
     gathered.fence()
     return gathered.local
+
+
+def host_b_bytes(b_host, world: int) -> int:
+    """Bytes of B this rank uploads in matmul_tma_host_sharded: its 1/world of the rows when K divides evenly
+    (the rest arrives over NVLink), else all of B."""
+    K = b_host.shape[0]
+    rows = K // world if K % world == 0 else K
+    return rows * b_host.shape[1] * b_host.element_size()
+
+
+def matmul_tma_host_sharded(a_shard, b, out_shard=None, group=None):
+    """This rank's rows of C = A.B for HOST operands on a box of several GPUs (one process per GPU).
+
+    `a_shard` is the rank's row block of A, `b` the whole of B, both host tensors (pinned for asynchronous
+    copies); the result lands in `out_shard` (host).  B crosses the host link once for the whole box: every
+    rank uploads K/world of its rows and the ranks all-gather them over NVLink (NCCL), instead of every rank
+    uploading all of B.  A's rows then stream to the GPU in row blocks while earlier blocks multiply and
+    finished rows of C stream back (ops' host pipeline).  Falls back to uploading all of B when K does not
+    divide by the number of ranks."""
+    import torch
+    import torch.distributed as dist
+    from . import ops
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    K, N = b.shape
+    device = torch.device("cuda", torch.cuda.current_device())
+    if K % world == 0:
+        rows = K // world
+        b_dev = torch.empty((K, N), dtype=b.dtype, device=device)
+        mine = b_dev[rank * rows:(rank + 1) * rows]
+        mine.copy_(b[rank * rows:(rank + 1) * rows], non_blocking=True)
+        dist.all_gather_into_tensor(b_dev, mine, group=group)
+    else:
+        b_dev = b.to(device, non_blocking=True)
+    return ops.matmul_tma_host_rows(a_shard, b_dev, out_shard)
