@@ -596,6 +596,24 @@ def test_attention_full_size_heads_against_oracle(causal):
     assert float((o1.float() - 1).abs().max()) <= 2 ** -7
 
 
+@pytest.mark.parametrize("Z,H,S,causal", [(1, 2, 512, False), (1, 3, 1024, True), (2, 2, 2048, True), (1, 5, 1536, False)])
+def test_attention_cta_pair_kernel_is_bit_identical(monkeypatch, Z, H, S, causal):
+    # the alternative kernel on CTA pairs (cta_group::2, four Q tiles per pair; selected with B200K_ATTN_2CTA=1 for
+    # HEAD_DIM 128 and N_CTX a multiple of 512): same arithmetic per row, so the same bits for O and M
+    D = 128
+    q, k, v = (t.cuda() for t in gi.attn_inputs(Z, H, S, D, seed=29))
+    monkeypatch.delenv("B200K_ATTN_2CTA", raising=False)
+    o1, m1 = ops.attention_with_lse(q, k, v, causal, D ** -0.5)
+    lib = _lib.load()
+    before = lib.b200k_launch_count()
+    monkeypatch.setenv("B200K_ATTN_2CTA", "1")
+    o2, m2 = ops.attention_with_lse(q, k, v, causal, D ** -0.5)
+    torch.cuda.synchronize()
+    assert lib.b200k_launch_count() - before == 1
+    assert torch.equal(o1.view(torch.int16), o2.view(torch.int16)) and torch.equal(m1.view(torch.int32), m2.view(torch.int32))
+    assert ops.device_status() == 0
+
+
 def test_attention_rejects_unsupported():
     q = torch.zeros(1, 1, 100, 128, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(NotImplementedError):

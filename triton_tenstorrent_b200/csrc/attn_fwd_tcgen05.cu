@@ -32,15 +32,14 @@
 #include <utility>
 #include <vector>
 
+#include "attn_common.cuh"
+#include "attn_fwd_2cta.cuh"
 #include "launch.h"
 #include "ptx.cuh"
 
 namespace b200k {
 
-constexpr int AT_BM = 128;            // rows per Q tile
-constexpr int AT_BN = 128;            // keys per K/V block
 constexpr int AT_THREADS = 384;         // three warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
-constexpr int AT_BOX_BYTES = 16384;   // one TMA box: 128 rows x 64 columns of bf16
 constexpr int AT_MAX_NSLOT = 3;       // K/V ring slots (2 for head dimension 256).  Measured at D = 128, S = 4096:
                                       // 3 slots 1269 / 1004 TFLOP/s (full / causal), 4: 1264 / 980, 5: 1253 / 970,
                                       // 2: 1223 / 1004 -- a deeper prefetch only adds traffic ahead of its use
@@ -66,8 +65,6 @@ struct AttnCfg {
   static_assert(SMEM_TOTAL <= 232448, "attention shared memory budget exceeded");
   static_assert(O_COL0 + NTILE * (D < 128 ? 128 : D) <= 512, "attention tensor memory budget exceeded");
 };
-
-constexpr float AT_RESCALE_THRESHOLD = 8.0f;  // log2 units
 
 // Two refinements of the softmax path, both measured at Z=4, H=32, N_CTX=4096 (non-causal TFLOP/s at HEAD_DIM 128 / 64;
 // with neither: 1261 / 683):
@@ -125,32 +122,6 @@ __device__ __forceinline__ int attn_round_item(const AttnParams& p, int k) {
   const int idx = k * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
   const int item = p.sched != nullptr ? __ldg(p.sched + idx) : idx;
   return item < p.num_items ? item : -1;
-}
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// In place: s[i] <- exp2(s[i] * scale - m) for 32 scores (fp32 bits), adding the results to two pair sums.
-// Pass 1: 16 packed multiply-subtracts; pass 2: 32 exponentials; pass 3: 16 packed adds.
-__device__ __forceinline__ void exp_block32(uint32_t (&s)[32], uint64_t scale2, uint64_t negm2, uint64_t& sum_a,
-                                            uint64_t& sum_b) {
-#pragma unroll
-  for (int c = 0; c < 16; ++c) {
-    float x0, x1;
-    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, negm2), x0, x1);
-    s[2 * c] = __float_as_uint(x0);
-    s[2 * c + 1] = __float_as_uint(x1);
-  }
-#pragma unroll
-  for (int c = 0; c < 32; ++c) s[c] = __float_as_uint(ex2_approx(__uint_as_float(s[c])));
-#pragma unroll
-  for (int c = 0; c < 16; c += 2) {
-    sum_a = add_f32x2(sum_a, pack_f32x2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])));
-    sum_b = add_f32x2(sum_b, pack_f32x2(__uint_as_float(s[2 * c + 2]), __uint_as_float(s[2 * c + 3])));
-  }
 }
 
 // 12 warps start with 168 registers each (16384 per scheduler partition / 96 threads).  The third
@@ -687,12 +658,12 @@ struct SchedTable {
 static std::map<SchedKey, SchedTable> g_sched;
 static std::mutex g_sched_mutex;
 
-// Host mirror of attn_item's block count for a causal item.
+// K/V blocks a causal item walks: its last Q tile's diagonal block is the last one (items hold ntile tiles:
+// 1 for head dimension 256, 2 in the single-CTA kernel, 4 in the CTA-pair kernel).
 static int causal_item_blocks(int item, int num_pairs, int num_mblk, int ntile) {
   const int pr = num_pairs - 1 - item % num_pairs;
-  const int m0 = ntile * pr, m1 = ntile * pr + 1;
-  const int n1 = (ntile == 2 && m1 < num_mblk) ? m1 + 1 : 0;
-  return n1 > m0 + 1 ? n1 : m0 + 1;
+  const int n = ntile * (pr + 1);
+  return n < num_mblk ? n : num_mblk;
 }
 
 std::vector<int> attn_schedule(int ZH, int num_pairs, int num_mblk, int ntile, int grid, int* rounds_out) {
@@ -768,8 +739,61 @@ static int get_schedule(const SchedKey& key, cudaStream_t stream, const int** de
   return B200K_OK;
 }
 
+// The CTA-pair kernel (attn_fwd_2cta.cuh): head dimension 128, whole groups of four Q tiles.
+// Not the default: it measures slightly slower than the single-CTA kernel (see the note in that file).
+static bool attn2_applies(const AttnArgs& a) {
+  if (a.D != A2_D || a.N_CTX % (4 * AT_BM) != 0) return false;
+  const char* e = getenv("B200K_ATTN_2CTA");
+  return e != nullptr && atoi(e) != 0;
+}
+
+static int attn2_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uint32_t* status, bool may_allocate) {
+  const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
+  CUtensorMap tq, tk, tv, to;
+  int rc;
+  if ((rc = make_tmap_bf16_2d(&tq, a.q, A2_D, rows, A2_D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tk, a.k, A2_D, rows, A2_D, 64, AT_BN / 2)) != 0) return rc;   // half of a block's keys
+  if ((rc = make_tmap_bf16_2d(&tv, a.v, A2_D, rows, A2_D, 64, AT_BN)) != 0) return rc;       // half of the columns
+  if ((rc = make_tmap_bf16_2d(&to, a.o, A2_D, rows, A2_D, 64, 32)) != 0) return rc;
+  ExtraMaps extra;
+  memset(&extra, 0, sizeof(extra));
+  for (int d = 0; d < a.n_extra; ++d)
+    if ((rc = make_tmap_bf16_2d(&extra.m[d], a.extra_o[d], A2_D, rows, A2_D, 64, 32)) != 0) return rc;
+
+  Attn2Params p;
+  p.ZH = a.Z * a.H;
+  p.N_CTX = a.N_CTX;
+  p.num_mblk = a.N_CTX / AT_BM;
+  p.num_quads = p.num_mblk / 4;
+  p.num_items = p.ZH * p.num_quads;
+  p.causal = a.causal ? 1 : 0;
+  p.qk_scale = a.sm_scale * 1.44269504f;
+  p.lse2 = a.lse2;
+  p.status = status;
+  p.n_extra = a.n_extra;
+
+  const int max_pairs = sm_count / 2;
+  int pairs = pick_grid(max_pairs, p.num_items, p.num_quads, p.causal != 0);
+  p.sched = nullptr;
+  p.rounds = (p.num_items + pairs - 1) / pairs;
+  const char* sched_env = getenv("B200K_ATTN_SCHEDULE");
+  if (p.causal && p.num_quads > 1 && may_allocate && !(sched_env != nullptr && atoi(sched_env) == 0)) {
+    pairs = p.num_items < max_pairs ? p.num_items : max_pairs;   // the table balances any grid: use every pair
+    int dev = 0;
+    B200K_CHECK_CUDA(cudaGetDevice(&dev));
+    if ((rc = get_schedule(SchedKey{dev, p.ZH, p.num_quads, p.num_mblk, 4, pairs}, stream, &p.sched, &p.rounds)) != 0) return rc;
+  }
+  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_bf16_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        A2_SMEM_TOTAL));
+  attn_fwd_bf16_tcgen05_2cta_kernel<<<2 * pairs, A2_THREADS, A2_SMEM_TOTAL, stream>>>(tq, tk, tv, to, extra, p);
+  count_launch();
+  B200K_CHECK_LAUNCH("attn_fwd_bf16_tcgen05_2cta_kernel");
+  return B200K_OK;
+}
+
 // Encodes the tensor maps and launches the kernel on `sm_count` SMs, reporting to `status`.
 static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uint32_t* status, bool may_allocate) {
+  if (attn2_applies(a) && sm_count >= 2) return attn2_launch(a, stream, sm_count, status, may_allocate);
   const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
   CUtensorMap tq, tk, tv, to;
   int rc;

@@ -593,7 +593,7 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
           // this warp's part of the accumulator has left tensor memory: tell the leader's MMA thread
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));
+          if (lane == 0) mbar_arrive_remote(mapa_shared(smem_u32(&tmem_empty_bar[acc]), 0));   // tensor-memory data only: CTA-scope release
         }
         epilogue_chunk(p, &tmap_c, extra.m, v0, v1, row, m0 + q * 32, n0 + c * 64, my_stage, buf, lane);
       }
