@@ -276,6 +276,15 @@ int b200k_attn_causal_schedule(int ZH, int N_CTX, int D, int ctas, int* table, i
 int b200k_block_range(int64_t num_blocks, int workers, int w, int64_t* block_start, int64_t* block_end);
 
 /*
+ * How b200k_matmul_bf16 runs the output tiles that are left over after the full waves of 256 x 256 tiles (host
+ * arithmetic only; it refines, below the block, the partition the reference's runtime makes by dealing whole
+ * blocks to cores, npu/lib/TritonNPUToTenstorrent/D2M/SPMDOpToD2M.cpp:77-113).  For an M x N x K problem on
+ * `sm_count` SMs out5 receives: mode (0 = whole tiles, 1 = each leftover tile as two column halves on twice as
+ * many CTA pairs), leftover tiles, CTA pairs, full waves, work items of the last wave.
+ */
+int b200k_matmul_tail_plan(int M, int N, int K, int sm_count, int* out5);
+
+/*
  * Reads (synchronously, after synchronising `stream`) the per-device status word that the
  * matmul/attention kernels set when one of their bounded waits gives up.  *code receives 0 when
  * healthy, else (site<<8 | role); the word is cleared.  Returns B200K_ERR_DEVICE_TIMEOUT if non-zero.

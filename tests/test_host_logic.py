@@ -236,3 +236,27 @@ def test_causal_attention_schedule_covers_and_balances(ZH, S, D, ctas):
         mine = [x for x in (t[k * ctas + c] for k in range(rounds.value)) if 0 <= x < (ZH - tail_heads) * pairs]
         assert mine == sorted(mine)
     assert lib.b200k_attn_causal_schedule(ZH, S, D, ctas, table, 0, ctypes.byref(rounds)) == _lib.ERR_INVALID_ARG
+
+
+def _tail_plan(M, N, K, sm_count=148):
+    import ctypes
+    out = (ctypes.c_int * 5)()
+    _lib.check(_lib.load().b200k_matmul_tail_plan(M, N, K, sm_count, out))
+    return dict(mode=out[0], rest=out[1], pairs=out[2], full_waves=out[3], last_wave_items=out[4])
+
+
+def test_matmul_tail_cost_model():
+    # the M-row shards of the 8192^3 problem over 1, 2, 4 and 8 GPUs (CTA pairs on 256 x 256 tiles, 74 pairs)
+    assert _tail_plan(8192, 8192, 8192) == dict(mode=0, rest=62, pairs=74, full_waves=13, last_wave_items=62)
+    assert _tail_plan(4096, 8192, 8192) == dict(mode=0, rest=68, pairs=74, full_waves=6, last_wave_items=68)
+    assert _tail_plan(2048, 8192, 8192) == dict(mode=1, rest=34, pairs=74, full_waves=3, last_wave_items=68)
+    assert _tail_plan(1024, 8192, 8192) == dict(mode=0, rest=54, pairs=74, full_waves=1, last_wave_items=54)
+    # the other sizes of the workload: 4096^3 (256 tiles) and 16384^3 (4096 tiles = 55 waves + 26)
+    assert _tail_plan(4096, 4096, 4096)["mode"] == 1 and _tail_plan(16384, 16384, 16384) == dict(
+        mode=1, rest=26, pairs=74, full_waves=55, last_wave_items=52)
+    # column halves only while they fit into one wave, never for an exact number of waves or a single partial wave
+    for M in range(256, 8192 + 1, 256):
+        plan = _tail_plan(M, 8192, 8192)
+        assert plan["mode"] == (1 if 0 < 2 * plan["rest"] <= plan["pairs"] and plan["rest"] < plan["pairs"] else 0)
+        assert plan["last_wave_items"] <= plan["pairs"]
+    assert _tail_plan(256, 512, 64, sm_count=148) == dict(mode=0, rest=0, pairs=2, full_waves=1, last_wave_items=0)

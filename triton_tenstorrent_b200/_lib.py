@@ -92,6 +92,7 @@ SIGNATURES = {
     "b200k_ipc_export": (c_int, [c_void_p, POINTER(IpcHandle)]),
     "b200k_ipc_open": (c_int, [POINTER(IpcHandle), POINTER(c_void_p)]),
     "b200k_block_range": (c_int, [c_int64, c_int, c_int, POINTER(c_int64), POINTER(c_int64)]),
+    "b200k_matmul_tail_plan": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int)]),
     "b200k_device_status": (c_int, [c_void_p, POINTER(c_uint32)]),
     "b200k_selftest_wait_timeout": (c_int, [c_int64, c_void_p]),
     "b200k_launch_count": (c_int64, []),

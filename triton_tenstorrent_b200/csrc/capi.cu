@@ -607,6 +607,13 @@ int b200k_block_range(int64_t num_blocks, int workers, int w, int64_t* block_sta
   return B200K_OK;
 }
 
+int b200k_matmul_tail_plan(int M, int N, int K, int sm_count, int* out5) {
+  clear_error();
+  if (M <= 0 || N <= 0 || K <= 0 || sm_count < 2 || out5 == nullptr)
+    return set_error(B200K_ERR_INVALID_ARG, "matmul_tail_plan: bad arguments");
+  return matmul_tail_plan(M, N, K, sm_count, out5);
+}
+
 int b200k_device_status(void* stream, uint32_t* code) {
   clear_error();
   const DeviceInfo* dev = current_device_info();

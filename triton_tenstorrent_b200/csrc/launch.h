@@ -90,6 +90,11 @@ struct MatmulArgs {
 // status_override: device word the kernel reports bounded-wait failures to (nullptr = the
 // per-device word from current_device_info()).
 int matmul_bf16(const MatmulArgs& a, cudaStream_t s, uint32_t* status_override);
+// How the CTA-pair matmul runs the `rest` tiles left after the full waves of `pairs` pairs: 0 = as whole tiles,
+// 1 = each cut in two column halves.  Pure host code.
+int matmul_tail_mode(int rest, int pairs);
+// out[0..5) = mode, leftover tiles, pairs, full waves, work items of the last wave.
+int matmul_tail_plan(int M, int N, int K, int sm_count, int* out);
 
 struct AttnArgs {
   const void* q;

@@ -694,6 +694,37 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   return B200K_OK;
 }
 
+// How the CTA-pair kernel runs the `rest` tiles left after the full waves of `pairs` pairs, from measured costs in
+// units of one whole-tile wave (M x 8192 x 8192 on one B200, whole / column halves):
+//   whole tiles     1     always possible
+//   column halves   each leftover tile as two 256 x 128 items on twice as many pairs; possible when 2 * rest <= pairs;
+//                   about 0.55-0.6 of a wave (M = 1280, 12 left: 135.1 -> 130.6 us; 2048, 34 left: 199.0 -> 186.1;
+//                   3072, 14 left: 291.3 -> 281.0)
+// A third form was built and measured and is NOT used: the leftover tiles' K blocks dealt out in equal shares, one per
+// pair, with fp32 partial sums through a workspace (M = 1024, 54 left: 99.8 -> 115.5 us; 8192, 62 left: 794 -> 838;
+// correct to 1 bf16 ulp, but the shares break the locality of all pairs sweeping K together, and two epilogues plus
+// the round trip through the workspace end up on the critical path).
+// Returns 0 = whole tiles, 1 = column halves.
+int matmul_tail_mode(int rest, int pairs) {
+  if (rest <= 0 || rest >= pairs) return 0;
+  return 2 * rest <= pairs ? 1 : 0;
+}
+
+int matmul_tail_plan(int M, int N, int K, int sm_count, int* out) {
+  const int tiles = ((M + 255) / 256) * ((N + MM2_BN - 1) / MM2_BN);
+  const int max_pairs = sm_count / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  const int rest = pairs > 0 ? tiles % pairs : 0;
+  const int mode = matmul_tail_mode(rest, pairs);
+  out[0] = mode;
+  out[1] = rest;
+  out[2] = pairs;
+  out[3] = tiles / (pairs > 0 ? pairs : 1);                  // full waves
+  out[4] = mode == 1 ? 2 * rest : rest;                      // work items of the last wave
+  (void)K;
+  return 0;
+}
+
 template <int STAGES>
 static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_t stream, uint32_t* status) {
   using L = Matmul2Smem<STAGES>;
@@ -735,7 +766,7 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   p.num_work = p.full_work = p.num_tiles;
   const int rest = p.num_tiles % pairs;
   const char* split_env = getenv("B200K_MATMUL_SPLIT_TAIL");
-  if (rest > 0 && 2 * rest <= pairs && !(split_env != nullptr && atoi(split_env) == 0)) {
+  if (matmul_tail_mode(rest, pairs) == 1 && !(split_env != nullptr && atoi(split_env) == 0)) {
     p.full_work = p.num_tiles - rest;
     p.num_work = p.full_work + 2 * rest;
   }
