@@ -142,8 +142,11 @@ int b200k_matmul_tile32(const void* A, const void* B, void* C, int M, int N, int
 /*
  * O = softmax(Q K^T * sm_scale [+ causal mask]) V per (batch, head); q,k,v,o bf16 contiguous
  * [Z,H,N_CTX,D]; lse2[Z,H,N_CTX] fp32 receives m_i + log2(l_i) (base-2 log-sum-exp of the
- * scaled scores), exactly the `M` tensor of the reference.  D must be 16, 32, 64, 128 or 256 (the reference's set, 06-fused-attention.py:233) and N_CTX a multiple of
- * 128 (b200k_attn_supported tells); the reference's other head sizes return B200K_ERR_UNSUPPORTED.
+ * scaled scores), exactly the `M` tensor of the reference.  D must be 16, 32, 64, 128 or 256 (the reference's set,
+ * 06-fused-attention.py:233); other head sizes return B200K_ERR_UNSUPPORTED (b200k_attn_supported tells).  N_CTX may
+ * be any length >= 1: the reference walks whole BLOCK_M x BLOCK_N blocks (32, 64 or 128 rows, :110-121) and is only
+ * meaningful for multiples of them; here keys past N_CTX are masked and rows past it are neither computed into M
+ * nor stored, so lengths such as 96, 192 or 320 (multiples of the reference's smaller blocks) and ragged ones work.
  * Replaces: _attn_fwd / _attn_fwd_inner, examples/fused-attn/06-fused-attention.py:33-90,143-215
  *           (host wrapper _attention.forward :224-273).
  */

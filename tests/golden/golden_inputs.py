@@ -32,6 +32,10 @@ ATTN_CASES = [
     (1, 2, 128, 16, True, 32, 16),
     (1, 2, 128, 32, False, 64, 32),
     (1, 1, 256, 256, True, 64, 64),
+    # sequence lengths that are multiples of the reference's smaller blocks but not of 128
+    (1, 2, 192, 128, True, 64, 64),
+    (1, 2, 320, 64, False, 64, 64),
+    (1, 1, 96, 32, True, 32, 32),
 ]
 
 

@@ -59,10 +59,10 @@ def test_argument_errors_before_any_device_work():
     assert lib.b200k_matmul_bf16(None, None, None, 0, 8, 8, 8, 8, 8, None, 0, 0, 0, 0, None) == _lib.ERR_INVALID_ARG
     assert lib.b200k_matmul_bf16(16, 16, 16, 8, 8, 8, 12, 8, 8, None, 0, 0, 0, 0, None) == _lib.ERR_INVALID_ARG
     assert "multiples of 8" in _lib.last_error()
-    assert lib.b200k_attn_fwd_bf16(16, 16, 16, 16, 16, 1, 1, 100, 128, 0, 0.1, None) == _lib.ERR_UNSUPPORTED
+    assert lib.b200k_attn_fwd_bf16(16, 16, 16, 16, 16, 1, 1, 128, 48, 0, 0.1, None) == _lib.ERR_UNSUPPORTED   # HEAD_DIM 48
     assert lib.b200k_attn_supported(128, 4096) == 1 and lib.b200k_attn_supported(64, 256) == 1
     assert lib.b200k_attn_supported(16, 128) == 1 and lib.b200k_attn_supported(256, 4096) == 1
-    assert lib.b200k_attn_supported(48, 4096) == 0 and lib.b200k_attn_supported(128, 200) == 0
+    assert lib.b200k_attn_supported(48, 4096) == 0 and lib.b200k_attn_supported(128, 200) == 1 and lib.b200k_attn_supported(128, 0) == 0
     assert lib.b200k_launch(b"no_such_kernel", 1, 1, 1, None, None, 0) == _lib.ERR_UNSUPPORTED
     assert lib.b200k_launch(b"add_kernel", 0, 1, 1, None, None, 0) == _lib.ERR_INVALID_ARG
     with pytest.raises(_lib.B200KError):

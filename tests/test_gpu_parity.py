@@ -614,10 +614,37 @@ def test_attention_cta_pair_kernel_is_bit_identical(monkeypatch, Z, H, S, causal
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("Z,H,S,D,causal", [(1, 2, 100, 128, False), (2, 3, 100, 128, True), (1, 2, 333, 128, False),
+                                            (1, 3, 333, 64, True), (1, 2, 1, 128, True), (1, 1, 129, 256, False),
+                                            (2, 2, 200, 32, True), (1, 2, 1000, 128, False), (1, 2, 1000, 128, True)])
+def test_attention_ragged_sequence_lengths(Z, H, S, D, causal):
+    # N_CTX that is not a multiple of the 128-row tiles: the last tile's rows past N_CTX are not stored and the last
+    # block's keys past N_CTX are masked.  O sits between canaries inside one buffer, M likewise.
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=31)
+    blk = 1
+    for b in (128, 64, 32, 25, 16, 9, 8, 4, 3, 2):       # an oracle block size that divides N_CTX (and <= HEAD_DIM)
+        if S % b == 0 and b <= D:
+            blk = b
+            break
+    ref_o, ref_m = oracle.attention(q, k, v, causal, D ** -0.5, BLOCK_M=blk, BLOCK_N=blk)
+    lib = _lib.load()
+    n = q.numel()
+    obuf = torch.full((n + 512,), -7.0, dtype=torch.bfloat16, device="cuda")
+    mbuf = torch.full((Z * H * S + 64,), -7.0, dtype=torch.float32, device="cuda")
+    o = obuf[256:256 + n].view(Z, H, S, D)
+    m = mbuf[32:32 + Z * H * S].view(Z, H, S)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    _lib.check(lib.b200k_attn_fwd_bf16(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), m.data_ptr(), Z, H, S, D,
+                                       int(causal), D ** -0.5, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert float((o.cpu().float() - ref_o.float()).abs().max()) <= ATTN_MAX_ABS
+    assert float((m.cpu() - ref_m).abs().max()) <= 1e-4
+    assert bool((obuf[:256] == -7.0).all()) and bool((obuf[256 + n:] == -7.0).all())
+    assert bool((mbuf[:32] == -7.0).all()) and bool((mbuf[32 + Z * H * S:] == -7.0).all())
+    assert ops.device_status() == 0
+
+
 def test_attention_rejects_unsupported():
-    q = torch.zeros(1, 1, 100, 128, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(NotImplementedError):
-        ops.attention(q, q, q, False, 0.1)
     q48 = torch.zeros(1, 1, 128, 48, dtype=torch.bfloat16, device="cuda")       # not in {16, 32, 64, 128, 256}
     with pytest.raises(AssertionError):
         ops.attention(q48, q48, q48, False, 0.1)

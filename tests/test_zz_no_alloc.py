@@ -134,5 +134,5 @@ def test_noalloc_rejects_problems_beyond_the_static_capacity():
     rc = lib.b200k_attn_fwd_bf16_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), 2 ** 31 - 1, 2 ** 31 - 1,
                                          2 ** 31 - 128, 128, 0, 0.1, None)
     assert rc == _lib.ERR_INVALID_ARG
-    rc = lib.b200k_attn_fwd_bf16_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), 1, 1, 100, 128, 0, 0.1, None)
+    rc = lib.b200k_attn_fwd_bf16_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), 1, 1, 128, 48, 0, 0.1, None)
     assert rc == _lib.ERR_UNSUPPORTED                           # same shape rules as the existing entry point

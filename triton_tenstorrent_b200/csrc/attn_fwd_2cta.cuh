@@ -514,6 +514,7 @@ attn_fwd_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_q, co
   }
 
   // -------------------------------------------------------------------- teardown
+  drain_after_abort(abort_smem);
   // Neither CTA may exit (or free tensor memory) while its partner can still signal its barriers.
   tc_fence_before();
   __syncthreads();

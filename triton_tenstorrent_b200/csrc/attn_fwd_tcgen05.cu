@@ -205,7 +205,6 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       const int item = attn_round_item(p, round);
       if (item < 0) continue;
       const AttnItem it = attn_item(p, item);
-      const int row_base = it.hz * p.N_CTX;
       for (int step = 0; ok && step < 2 * it.n; ++step) {
         // Q tiles are interleaved with the first K/V blocks: Q0 K0 Q1 V0 K1 V1 ...
         if (step < 2 && it.nblk[step] > 0) {
@@ -214,10 +213,10 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           if (!ok) break;
           if (lane == 0) {
             mbar_expect_tx(&q_full[t], Cfg::TX_BYTES);
-            const int row = row_base + it.mblk[t] * AT_BM;
+            const int row = it.mblk[t] * AT_BM;   // within the (batch, head): rows past N_CTX are zero-filled
 #pragma unroll
             for (int bx = 0; bx < Cfg::NBOX; ++bx)
-              tma_load_2d(smem_q + t * AT_TILE_BYTES + bx * AT_BOX_BYTES, &tmap_q, &q_full[t], bx * 64, row);
+              tma_load_3d(smem_q + t * AT_TILE_BYTES + bx * AT_BOX_BYTES, &tmap_q, &q_full[t], bx * 64, row, it.hz);
           }
           __syncwarp();
           ++q_loads[t];
@@ -229,10 +228,10 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         if (lane == 0) {
           mbar_expect_tx(&kv_full[slot], Cfg::TX_BYTES);
           const CUtensorMap* tm = is_v ? &tmap_v : &tmap_k;
-          const int row = row_base + j * AT_BN;
+          const int row = j * AT_BN;
           uint8_t* dst = smem_kv + slot * AT_TILE_BYTES;
 #pragma unroll
-          for (int bx = 0; bx < Cfg::NBOX; ++bx) tma_load_2d(dst + bx * AT_BOX_BYTES, tm, &kv_full[slot], bx * 64, row);
+          for (int bx = 0; bx < Cfg::NBOX; ++bx) tma_load_3d(dst + bx * AT_BOX_BYTES, tm, &kv_full[slot], bx * 64, row, it.hz);
         }
         __syncwarp();
         if (++slot == AT_NSLOT) { slot = 0; slot_phase ^= 1u; }
@@ -386,19 +385,24 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         tmem_ld_x32(t_s + 64, s2);
         tmem_ld_x32(t_s + 96, s3);
         tmem_wait_ld();
-        if (p.causal && j == n_me - 1) {
-          // diagonal block: key index > query index is masked (reference adds -1e6 before the max;
-          // after exp2 both give exactly 0)
+        // Keys of this block a row may see: all 128, except in the diagonal block of a causal launch (key index >
+        // query index is masked: the reference adds -1e6 before the max, after exp2 both give exactly 0) and in the
+        // last block of a head whose N_CTX is not a multiple of 128 (the keys past N_CTX do not exist; their scores
+        // come from zero-filled K rows).  `lim` >= 1 in both cases, so no row is ever fully masked.
+        int lim = AT_BN;
+        if (p.causal && j == n_me - 1) lim = r + 1;
+        if (p.N_CTX - j * AT_BN < lim) lim = p.N_CTX - j * AT_BN;
+        const bool masked = __any_sync(0xFFFFFFFFu, lim < AT_BN);
+        if (masked) {
           const uint32_t ninf = 0xFF800000u;
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
-            if (c > r) s0[c] = ninf;
-            if (c + 32 > r) s1[c] = ninf;
-            if (c + 64 > r) s2[c] = ninf;
-            if (c + 96 > r) s3[c] = ninf;
+            if (c >= lim) s0[c] = ninf;
+            if (c + 32 >= lim) s1[c] = ninf;
+            if (c + 64 >= lim) s2[c] = ninf;
+            if (c + 96 >= lim) s3[c] = ninf;
           }
         }
-        const bool diag = p.causal && j == n_me - 1;
         const uint64_t scale2 = pack_f32x2(scale, scale);
         uint64_t negm2 = pack_f32x2(-m_used, -m_used);
         uint64_t sum_a = 0, sum_b = 0;  // bit pattern of (0.f, 0.f)
@@ -473,10 +477,10 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
           // redo the first 32 exponentials with the new base: their scores are still in tensor memory
           tmem_ld_x32(t_s + 0, s0);
           tmem_wait_ld();
-          if (diag) {
+          if (masked) {
 #pragma unroll
             for (int c = 0; c < 32; ++c)
-              if (c > r) s0[c] = 0xFF800000u;
+              if (c >= lim) s0[c] = 0xFF800000u;
           }
           sum_a = 0;
           sum_b = 0;
@@ -569,18 +573,22 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         }
       }
       tc_fence_before();
-      const int64_t out_row = static_cast<int64_t>(it.hz) * p.N_CTX + it.mblk[t] * AT_BM;
-      p.lse2[out_row + r] = m_used + log2f(l);
+      const int row_in_head = it.mblk[t] * AT_BM;
+      if (row_in_head + r < p.N_CTX)    // the last tile of a head may run past N_CTX: those rows do not exist
+        p.lse2[static_cast<int64_t>(it.hz) * p.N_CTX + row_in_head + r] = m_used + log2f(l);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        const int y = static_cast<int>(out_row) + q * 32;
-#pragma unroll
-        for (int bx = 0; bx < Cfg::NBOX; ++bx) tma_store_2d(&tmap_o, stage + bx * AT_BOX_BYTES + q * 32 * 128, bx * 64, y);
-        for (int d = 0; d < p.n_extra; ++d) {
+        const int y = row_in_head + q * 32;   // rows past N_CTX are clipped by the store
+        if (y < p.N_CTX) {
 #pragma unroll
           for (int bx = 0; bx < Cfg::NBOX; ++bx)
-            tma_store_2d(&extra.m[d], stage + bx * AT_BOX_BYTES + q * 32 * 128, bx * 64, y);
+            tma_store_3d(&tmap_o, stage + bx * AT_BOX_BYTES + q * 32 * 128, bx * 64, y, it.hz);
+          for (int d = 0; d < p.n_extra; ++d) {
+#pragma unroll
+            for (int bx = 0; bx < Cfg::NBOX; ++bx)
+              tma_store_3d(&extra.m[d], stage + bx * AT_BOX_BYTES + q * 32 * 128, bx * 64, y, it.hz);
+          }
         }
         tma_store_commit();
         tma_store_wait_read<0>();
@@ -593,6 +601,7 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
   }
 
   // -------------------------------------------------------------------- teardown
+  drain_after_abort(abort_smem);
   tc_fence_before();
   __syncthreads();
   if (warp_idx == 9) {
@@ -603,7 +612,10 @@ attn_fwd_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
 
 int attn_supported(int D, int N_CTX) {
   const bool d_ok = D == 16 || D == 32 || D == 64 || D == 128 || D == 256;   // the reference's set (06-fused-attention.py:233)
-  return (d_ok && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0;
+  // any sequence length: tensor maps are per (batch, head), so tiles and blocks that run past N_CTX are zero-filled
+  // on loads, clipped on stores, and their keys masked (the reference itself walks whole BLOCK_M / BLOCK_N blocks
+  // and is only meaningful for multiples of them: 32, 64 or 128 depending on the configuration it picks, :110-121)
+  return (d_ok && N_CTX >= 1) ? 1 : 0;
 }
 
 static int pick_grid(int sm_count, int num_items, int num_pairs, bool causal) {
@@ -621,7 +633,7 @@ static int pick_grid(int sm_count, int num_items, int num_pairs, bool causal) {
 static int attn_check_args(const AttnArgs& a) {
   if (a.Z <= 0 || a.H <= 0 || a.N_CTX <= 0) return set_error(B200K_ERR_INVALID_ARG, "attention: Z, H, N_CTX must be positive");
   if (!attn_supported(a.D, a.N_CTX))
-    return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 16, 32, 64, 128 or 256; N_CTX a multiple of 128)", a.D, a.N_CTX);
+    return set_error(B200K_ERR_UNSUPPORTED, "attention: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 16, 32, 64, 128 or 256; N_CTX >= 1)", a.D, a.N_CTX);
   if (a.q == nullptr || a.k == nullptr || a.v == nullptr || a.o == nullptr || a.lse2 == nullptr)
     return set_error(B200K_ERR_INVALID_ARG, "attention: null pointer");
   if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
@@ -794,24 +806,25 @@ static int attn2_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, ui
 // Encodes the tensor maps and launches the kernel on `sm_count` SMs, reporting to `status`.
 static int attn_launch(const AttnArgs& a, cudaStream_t stream, int sm_count, uint32_t* status, bool may_allocate) {
   if (attn2_applies(a) && sm_count >= 2) return attn2_launch(a, stream, sm_count, status, may_allocate);
-  const int64_t rows = static_cast<int64_t>(a.Z) * a.H * a.N_CTX;
   CUtensorMap tq, tk, tv, to;
   int rc;
   const uint64_t D = static_cast<uint64_t>(a.D);
   const uint32_t box_cols = a.D >= 64 ? 64u : static_cast<uint32_t>(a.D);
-  if ((rc = make_tmap_bf16_2d(&tq, a.q, D, rows, D, box_cols, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tk, a.k, D, rows, D, box_cols, AT_BN)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tv, a.v, D, rows, D, box_cols, AT_BN)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&to, a.o, D, rows, D, box_cols, 32)) != 0) return rc;
+  // [Z*H][N_CTX][D]: one tensor-map "batch" entry per (batch, head)
+  const uint64_t zh = static_cast<uint64_t>(a.Z) * a.H, n_ctx = static_cast<uint64_t>(a.N_CTX);
+  if ((rc = make_tmap_bf16_3d(&tq, a.q, D, n_ctx, zh, box_cols, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_3d(&tk, a.k, D, n_ctx, zh, box_cols, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_3d(&tv, a.v, D, n_ctx, zh, box_cols, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_3d(&to, a.o, D, n_ctx, zh, box_cols, 32)) != 0) return rc;
   ExtraMaps extra;
   memset(&extra, 0, sizeof(extra));
   for (int d = 0; d < a.n_extra; ++d)
-    if ((rc = make_tmap_bf16_2d(&extra.m[d], a.extra_o[d], D, rows, D, box_cols, 32)) != 0) return rc;
+    if ((rc = make_tmap_bf16_3d(&extra.m[d], a.extra_o[d], D, n_ctx, zh, box_cols, 32)) != 0) return rc;
 
   AttnParams p;
   p.ZH = a.Z * a.H;
   p.N_CTX = a.N_CTX;
-  p.num_mblk = a.N_CTX / AT_BM;
+  p.num_mblk = (a.N_CTX + AT_BM - 1) / AT_BM;
   p.ntile = a.D <= 128 ? 2 : 1;
   p.num_pairs = (p.num_mblk + p.ntile - 1) / p.ntile;
   p.num_items = p.ZH * p.num_pairs;

@@ -156,6 +156,42 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return B200K_OK;
 }
 
+int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
+                      uint32_t box_inner, uint32_t box_rows) {
+  TmapKey key{reinterpret_cast<uintptr_t>(base), inner, rows, batch, box_inner, box_rows, 3};
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    auto it = g_tmaps.find(key);
+    if (it != g_tmaps.end()) {
+      *out = it->second;
+      return B200K_OK;
+    }
+  }
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) return set_error(B200K_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (inner * 2) % 16 != 0)
+    return set_error(B200K_ERR_INVALID_ARG, "tensor map: base and row pitch must be 16-byte aligned");
+  if (box_inner == 0 || box_inner * 2 > 128 || (box_inner * 2) % 16 != 0 || box_rows == 0 || box_rows > 256)
+    return set_error(B200K_ERR_INVALID_ARG, "tensor map: box %ux%u not supported", box_inner, box_rows);
+  cuuint64_t dims[3] = {inner, rows, batch};
+  cuuint64_t strides[2] = {inner * 2, rows * inner * 2};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(B200K_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d (dims %llu x %llu x %llu, box %u x %u)",
+                     static_cast<int>(r), (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)batch,
+                     box_inner, box_rows);
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    if (g_tmaps.size() > 4096) g_tmaps.clear();
+    g_tmaps.emplace(key, *out);
+  }
+  return B200K_OK;
+}
+
 int make_tmap_tile32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows,
                      bool row_pairs) {
   const uint32_t box_cols = 32;
@@ -491,7 +527,7 @@ int b200k_attn_causal_schedule(int ZH, int N_CTX, int D, int ctas, int* table, i
   if (ZH <= 0 || ctas <= 0 || table == nullptr || rounds == nullptr || !attn_supported(D, N_CTX))
     return set_error(B200K_ERR_INVALID_ARG, "attn_causal_schedule: bad arguments");
   const int ntile = D <= 128 ? 2 : 1;
-  const int num_mblk = N_CTX / 128;
+  const int num_mblk = (N_CTX + 127) / 128;
   const int num_pairs = (num_mblk + ntile - 1) / ntile;
   int r = 0;
   const std::vector<int> t = attn_schedule(ZH, num_pairs, num_mblk, ntile, ctas, &r);

@@ -45,6 +45,11 @@ void count_launch();
 // out-of-bounds reads fill with zero.  Cached per (base, dims, pitch, box).
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                       uint32_t box_inner, uint32_t box_outer);
+// 3-D bf16 tensor map of a contiguous [batch][rows][inner] tensor, box = 1 x box_rows x box_inner, 128-byte swizzle.
+// A box that runs past `rows` is zero-filled on loads and clipped on stores, so that it never touches the next
+// batch entry.
+int make_tmap_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
+                      uint32_t box_inner, uint32_t box_rows);
 // 4-D tensor map of a `rows` x `cols` matrix stored tile-major (contiguous 32 x 32 tiles, tiles in
 // row-major order; rows and cols multiples of 32): dimensions (column in tile, tile column, row in
 // tile, tile row), box = box_rows x 32 elements (one tile column, box_rows a multiple of 32),

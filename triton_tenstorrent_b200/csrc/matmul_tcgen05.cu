@@ -377,6 +377,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __g
   }
 
   // ------------------------------------------------------------------ teardown
+  drain_after_abort(abort_smem);
   tc_fence_before();
   __syncthreads();
   if (warp_idx == 1) {
@@ -603,6 +604,7 @@ matmul_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, cons
   }
 
   // ------------------------------------------------------------------ teardown
+  drain_after_abort(abort_smem);
   // Neither CTA may exit (or free tensor memory) while its partner can still signal its barriers.
   tc_fence_before();
   __syncthreads();

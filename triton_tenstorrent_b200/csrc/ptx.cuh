@@ -111,6 +111,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+// After a bounded wait has given up, a CTA must not free its tensor memory or exit while copies and MMAs it issued
+// earlier may still be in flight: nothing can be waited for any more (their barriers are what failed), so every thread
+// simply lets a fixed time pass (about 100 us, far longer than any single copy or MMA takes) before the teardown.
+__device__ __forceinline__ void drain_after_abort(const volatile uint32_t* abort_flag) {
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Proxy fences
 // ---------------------------------------------------------------------------------------------
@@ -135,6 +144,19 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+// Three coordinates (x innermost): used for tensors seen as [batch][row][column] so that a box that runs past the
+// rows of one batch entry is zero-filled on loads and clipped on stores instead of touching the next entry.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
 // Tile-major ("tilized") operands: the matrix is stored as contiguous 32 x 32 element tiles, tiles in

@@ -418,8 +418,7 @@ def attention_with_lse(q, k, v, causal, sm_scale, warp_specialize: bool = True):
     lib = _lib.load()
     Z, H, N_CTX, D = q.shape
     if not lib.b200k_attn_supported(D, N_CTX):
-        raise NotImplementedError(f"attention: no sm_100a kernel for HEAD_DIM={D}, N_CTX={N_CTX} "
-                                  "(N_CTX must be a multiple of 128)")
+        raise NotImplementedError(f"attention: no sm_100a kernel for HEAD_DIM={D}, N_CTX={N_CTX}")
     qd, kd, vd = (_to_device(t).contiguous() for t in (q, k, v))
     o = torch.empty_like(qd)
     M = torch.empty((Z, H, N_CTX), device=qd.device, dtype=torch.float32)
