@@ -203,6 +203,22 @@ int b200k_attn_fwd_bf16_multi(const void* q, const void* k, const void* v, void*
 int b200k_attn_supported(int D, int N_CTX);
 
 /*
+ * Attention backward: dq, dk, dv (bf16, contiguous [Z,H,N_CTX,D]) from q, k, v, the forward's o and lse2 (its `M`
+ * output) and the gradient d_o of o.  This is the consumer of what the reference's forward saves for a backward pass,
+ * `ctx.save_for_backward(q, k, v, o, M)` (examples/fused-attn/06-fused-attention.py:238,269); the reference itself has
+ * no backward kernel, so there is no reference function this replaces: the algorithm is that of the Triton tutorial the
+ * reference's forward comes from (delta = rowsum(o * d_o); P recomputed as exp2(qk_scale * q.k - M); dv = P^T d_o;
+ * dS = P (d_o.v - delta); dk = sm_scale dS^T q; dq = sm_scale dS k), with P and dS rounded to bf16 where they enter a
+ * tensor-core product and everything else in fp32.  delta_scratch: Z*H*N_CTX floats the caller provides (the
+ * library allocates nothing).  D must be 128 and N_CTX a multiple of 128 (b200k_attn_bwd_supported tells); every
+ * buffer 16-byte aligned.  Three kernel launches on `stream`, deterministic (no atomics).
+ */
+int b200k_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
+                        void* dq, void* dk, void* dv, float* delta_scratch, int Z, int H, int N_CTX, int D, int causal,
+                        float sm_scale, void* stream);
+int b200k_attn_bwd_supported(int D, int N_CTX);
+
+/*
  * Generic launch mirroring the argument list the reference launcher builds
  * (backend/driver.py:98-170 TTLauncher.__call__: constexprs dropped, tensors as pointers,
  * TensorDescriptor flattened to base, shape.., strides.., padding flag, shape.., strides..).

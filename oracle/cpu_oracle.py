@@ -56,6 +56,8 @@ def load() -> ctypes.CDLL:
     lib.oracle_matmul_kernel_tile32.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int]
     lib.oracle_attn_fwd_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                          c_int, c_float, c_int, c_int]
+    lib.oracle_attn_bwd_bf16.argtypes = [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_int, c_float]
+    lib.oracle_attn_bwd_bf16.restype = None
     for fn in ("oracle_block_range", "oracle_add_f32", "oracle_add_loop", "oracle_sin_f32", "oracle_sin_f64_to_f32", "oracle_mul_add_f32",
                "oracle_golden_matmul", "oracle_golden_matmul_naive", "oracle_matmul_kernel_tile32", "oracle_attn_fwd_bf16"):
         getattr(lib, fn).restype = None
@@ -198,6 +200,19 @@ def attention(q, k, v, causal: bool, sm_scale: float, BLOCK_M: int = 128, BLOCK_
     load().oracle_attn_fwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), M.data_ptr(), Z, H, S, D,
                                 1 if causal else 0, float(sm_scale), BLOCK_M, BLOCK_N)
     return o, M
+
+
+def attention_backward(q, k, v, o, d_o, M, causal: bool, sm_scale: float):
+    """(dq, dk, dv) bf16 from q, k, v, the forward's o and M, and the gradient of o.  PARITY UNPINNED: the reference has
+    no backward kernel; this restates the Triton tutorial's algorithm in the forward's conventions (see oracle.c)."""
+    q, k, v, o, d_o = (_cpu(t, torch.bfloat16) for t in (q, k, v, o, d_o))
+    M = _cpu(M, torch.float32)
+    Z, H, S, D = q.shape
+    assert D <= 256
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    load().oracle_attn_bwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), M.data_ptr(),
+                                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), Z, H, S, D, 1 if causal else 0, float(sm_scale))
+    return dq, dk, dv
 
 
 # ---- error metrics used by the parity tests -----------------------------------------------------

@@ -404,3 +404,78 @@ void oracle_attn_fwd_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* 
     }
   }
 }
+
+/* ------------------------------------------------------------------------------------------- */
+/* Fused attention backward.  PARITY UNPINNED: the reference has no backward kernel (its forward */
+/* only saves q, k, v, o, M: examples/fused-attn/06-fused-attention.py:238,269), so there is no   */
+/* reference output or golden vector to pin this against.  It restates the algorithm of the      */
+/* Triton tutorial the reference's forward comes from, in the forward's conventions:             */
+/*   delta_i = sum_d o_id do_id;  p_ij = exp2(qk_scale * q_i.k_j - M_i)  (0 above the diagonal)   */
+/*   dv_j = sum_i bf16(p_ij) do_i;  ds_ij = p_ij (do_i.v_j - delta_i)                             */
+/*   dk_j = sm_scale sum_i bf16(ds_ij) q_i;  dq_i = sm_scale sum_j bf16(ds_ij) k_j                */
+/* all sums in fp32, one round-to-nearest-even downcast of each gradient at the end.             */
+/* The tests check it against fp32 automatic differentiation of the attention definition.        */
+/* ------------------------------------------------------------------------------------------- */
+void oracle_attn_bwd_bf16(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* o, const uint16_t* d_o,
+                          const float* M, uint16_t* dq, uint16_t* dk, uint16_t* dv, int Z, int H, int N_CTX, int D,
+                          int causal, float sm_scale) {
+  float qk_scale = sm_scale;
+  qk_scale *= 1.44269504f;
+  const size_t rows = (size_t)Z * H * N_CTX;
+  float* delta = (float*)malloc(rows * sizeof(float));
+#pragma omp parallel for schedule(static)
+  for (long long r = 0; r < (long long)rows; ++r) {
+    float s = 0.f;
+    for (int d = 0; d < D; ++d) s += bf16_to_f32(o[r * D + d]) * bf16_to_f32(d_o[r * D + d]);
+    delta[r] = s;
+  }
+  /* pass over the keys: dk_j, dv_j */
+#pragma omp parallel for collapse(2) schedule(dynamic, 8)
+  for (int hz = 0; hz < Z * H; ++hz) {
+    for (int j = 0; j < N_CTX; ++j) {
+      const size_t base = (size_t)hz * N_CTX;
+      float accv[256], acck[256];
+      for (int d = 0; d < D; ++d) { accv[d] = 0.f; acck[d] = 0.f; }
+      for (int i = causal ? j : 0; i < N_CTX; ++i) {
+        float s = 0.f, dp = 0.f;
+        for (int d = 0; d < D; ++d) {
+          s += bf16_to_f32(q[(base + i) * D + d]) * bf16_to_f32(k[(base + j) * D + d]);
+          dp += bf16_to_f32(d_o[(base + i) * D + d]) * bf16_to_f32(v[(base + j) * D + d]);
+        }
+        const float p = exp2f(s * qk_scale - M[base + i]);
+        const float ds = p * (dp - delta[base + i]);
+        const float pb = bf16_to_f32(f32_to_bf16(p)), dsb = bf16_to_f32(f32_to_bf16(ds));
+        for (int d = 0; d < D; ++d) {
+          accv[d] += pb * bf16_to_f32(d_o[(base + i) * D + d]);
+          acck[d] += dsb * bf16_to_f32(q[(base + i) * D + d]);
+        }
+      }
+      for (int d = 0; d < D; ++d) {
+        dv[(base + j) * D + d] = f32_to_bf16(accv[d]);
+        dk[(base + j) * D + d] = f32_to_bf16(acck[d] * sm_scale);
+      }
+    }
+  }
+  /* pass over the queries: dq_i */
+#pragma omp parallel for collapse(2) schedule(dynamic, 8)
+  for (int hz = 0; hz < Z * H; ++hz) {
+    for (int i = 0; i < N_CTX; ++i) {
+      const size_t base = (size_t)hz * N_CTX;
+      float accq[256];
+      for (int d = 0; d < D; ++d) accq[d] = 0.f;
+      const int j_end = causal ? i + 1 : N_CTX;
+      for (int j = 0; j < j_end; ++j) {
+        float s = 0.f, dp = 0.f;
+        for (int d = 0; d < D; ++d) {
+          s += bf16_to_f32(q[(base + i) * D + d]) * bf16_to_f32(k[(base + j) * D + d]);
+          dp += bf16_to_f32(d_o[(base + i) * D + d]) * bf16_to_f32(v[(base + j) * D + d]);
+        }
+        const float p = exp2f(s * qk_scale - M[base + i]);
+        const float dsb = bf16_to_f32(f32_to_bf16(p * (dp - delta[base + i])));
+        for (int d = 0; d < D; ++d) accq[d] += dsb * bf16_to_f32(k[(base + j) * D + d]);
+      }
+      for (int d = 0; d < D; ++d) dq[(base + i) * D + d] = f32_to_bf16(accq[d] * sm_scale);
+    }
+  }
+  free(delta);
+}

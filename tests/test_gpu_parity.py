@@ -644,6 +644,95 @@ def test_attention_ragged_sequence_lengths(Z, H, S, D, causal):
     assert ops.device_status() == 0
 
 
+# ------------------------------------------------------------------------------------------------ attention backward
+def _d_o(Z, H, S, D, seed=33):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.randn(Z, H, S, D, generator=g, dtype=torch.float32).bfloat16()
+
+
+def _autograd_truth(q, k, v, d_o, causal, scale):
+    """fp32 automatic differentiation of the attention definition, on the GPU."""
+    qf, kf, vf = (t.cuda().float().requires_grad_(True) for t in (q, k, v))
+    sc = (qf @ kf.transpose(-1, -2)) * scale
+    if causal:
+        S = q.shape[-2]
+        sc = sc.masked_fill(~torch.ones(S, S, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    (torch.softmax(sc, dim=-1) @ vf).backward(d_o.cuda().float())
+    return qf.grad, kf.grad, vf.grad
+
+
+@pytest.mark.parametrize("Z,H,S,causal", [(1, 1, 128, False), (1, 1, 128, True), (1, 2, 256, False), (1, 3, 512, True),
+                                          (2, 2, 1024, False), (1, 2, 1024, True), (3, 5, 384, True)])
+def test_attention_backward_oracle(Z, H, S, causal):
+    # dq, dk, dv against the CPU oracle (parity unpinned: the reference has no backward) and against fp32 autograd
+    D = 128
+    scale = D ** -0.5
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=32)
+    d_o = _d_o(Z, H, S, D)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o, m = ops.attention_with_lse(qd, kd, vd, causal, scale)
+    lib = _lib.load()
+    before = lib.b200k_launch_count()
+    dq, dk, dv = ops.attention_backward(qd, kd, vd, o, m, d_o.cuda(), causal, scale)
+    torch.cuda.synchronize()
+    assert lib.b200k_launch_count() - before == 3            # delta, dK/dV, dQ
+    ref = oracle.attention_backward(q, k, v, o.cpu(), d_o, m.cpu(), causal, scale)
+    truth = _autograd_truth(q, k, v, d_o, causal, scale)
+    for name, got, r, t in zip(("dq", "dk", "dv"), (dq, dk, dv), ref, truth):
+        assert not torch.isnan(got.float()).any(), name
+        assert oracle.rel_frobenius(got.cpu().float(), r.float()) <= 1e-2, name
+        assert float((got.cpu().float() - r.float()).abs().max()) <= 3e-2, name
+        assert float((got.float() - t).norm() / t.norm()) <= 1e-2, name
+    assert ops.device_status() == 0
+
+
+def test_attention_backward_through_autograd_and_determinism():
+    # ops.attention is differentiable (the reference's _attention function with the backward it lacks); two runs give
+    # the same bits (no atomics anywhere)
+    Z, H, S, D = 1, 4, 512, 128
+    q, k, v = (t.cuda().requires_grad_(True) for t in gi.attn_inputs(Z, H, S, D, seed=34))
+    d_o = _d_o(Z, H, S, D).cuda()
+    grads = []
+    for _ in range(2):
+        o = ops.attention(q, k, v, True, D ** -0.5)
+        gq, gk, gv = torch.autograd.grad(o, (q, k, v), d_o)
+        grads.append((gq, gk, gv))
+    for a, b in zip(*grads):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    truth = _autograd_truth(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), d_o.cpu(), True, D ** -0.5)
+    for got, t in zip(grads[0], truth):
+        assert float((got.float() - t).norm() / t.norm()) <= 1e-2
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_backward_full_size_heads(causal):
+    # the full workload on the GPU; three (batch, head) pairs against fp32 autograd, canaries around the outputs
+    Z, H, S, D = 4, 32, 4096, 128
+    scale = D ** -0.5
+    q, k, v = (t.cuda() for t in gi.attn_inputs(Z, H, S, D, seed=35))
+    d_o = _d_o(Z, H, S, D).cuda()
+    o, m = ops.attention_with_lse(q, k, v, causal, scale)
+    dq, dk, dv = ops.attention_backward(q, k, v, o, m, d_o, causal, scale)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    for (z, h) in ((0, 0), (2, 13), (3, 31)):
+        sl = (slice(z, z + 1), slice(h, h + 1))
+        truth = _autograd_truth(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), d_o[sl].cpu(), causal, scale)
+        for name, got, t in zip(("dq", "dk", "dv"), (dq, dk, dv), truth):
+            assert float((got[sl].float() - t).norm() / t.norm()) <= 1e-2, (name, z, h)
+
+
+def test_attention_backward_rejects_unsupported():
+    q = torch.zeros(1, 1, 256, 64, dtype=torch.bfloat16, device="cuda")
+    m = torch.zeros(1, 1, 256, device="cuda")
+    with pytest.raises(NotImplementedError):
+        ops.attention_backward(q, q, q, q, m, q, False, 0.1)          # HEAD_DIM 64
+    q = torch.zeros(1, 1, 192, 128, dtype=torch.bfloat16, device="cuda")
+    m = torch.zeros(1, 1, 192, device="cuda")
+    with pytest.raises(NotImplementedError):
+        ops.attention_backward(q, q, q, q, m, q, False, 0.1)          # N_CTX not a multiple of 128
+
+
 def test_attention_rejects_unsupported():
     q48 = torch.zeros(1, 1, 128, 48, dtype=torch.bfloat16, device="cuda")       # not in {16, 32, 64, 128, 256}
     with pytest.raises(AssertionError):

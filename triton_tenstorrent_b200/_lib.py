@@ -87,6 +87,8 @@ SIGNATURES = {
                                           c_int, c_int, c_int, c_float, c_void_p]),
     "b200k_attn_causal_schedule": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int), c_int, POINTER(c_int)]),
     "b200k_attn_supported": (c_int, [c_int, c_int]),
+    "b200k_attn_bwd_bf16": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "b200k_attn_bwd_supported": (c_int, [c_int, c_int]),
     "b200k_launch": (c_int, [c_char_p, c_int, c_int, c_int, c_void_p, POINTER(Arg), c_int]),
     "b200k_device_props": (c_int, [c_int, POINTER(Props)]),
     "b200k_ipc_export": (c_int, [c_void_p, POINTER(IpcHandle)]),

@@ -18,7 +18,7 @@ CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libb200kernels.so"
 BUILD_DIR = PKG_DIR / "build"
 
-SOURCES = ["capi.cu", "elementwise.cu", "matmul_tcgen05.cu", "attn_fwd_tcgen05.cu", "selftest.cu"]
+SOURCES = ["capi.cu", "elementwise.cu", "matmul_tcgen05.cu", "attn_fwd_tcgen05.cu", "attn_bwd_tcgen05.cu", "selftest.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17",

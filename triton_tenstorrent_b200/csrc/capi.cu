@@ -540,6 +540,16 @@ int b200k_attn_causal_schedule(int ZH, int N_CTX, int D, int ctas, int* table, i
 
 int b200k_attn_supported(int D, int N_CTX) { return attn_supported(D, N_CTX); }
 
+int b200k_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
+                        void* dq, void* dk, void* dv, float* delta_scratch, int Z, int H, int N_CTX, int D, int causal,
+                        float sm_scale, void* stream) {
+  clear_error();
+  AttnBwdArgs a{q, k, v, o, d_o, lse2, dq, dk, dv, delta_scratch, Z, H, N_CTX, D, causal, sm_scale};
+  return attn_bwd_bf16(a, static_cast<cudaStream_t>(stream));
+}
+
+int b200k_attn_bwd_supported(int D, int N_CTX) { return attn_bwd_supported(D, N_CTX); }
+
 int b200k_launch(const char* kernel_name, int grid_x, int grid_y, int grid_z, void* stream, const b200k_arg* args,
                  int nargs) {
   clear_error();

@@ -114,6 +114,23 @@ struct AttnArgs {
   int n_extra;
 };
 int attn_fwd_bf16(const AttnArgs& a, cudaStream_t s);
+struct AttnBwdArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* lse2;   // M of the forward
+  void* dq;
+  void* dk;
+  void* dv;
+  float* delta;        // caller-provided scratch, Z*H*N_CTX floats
+  int Z, H, N_CTX, D;
+  int causal;
+  float sm_scale;
+};
+int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t s);
+int attn_bwd_supported(int D, int N_CTX);
 int attn_supported(int D, int N_CTX);
 // Work-queue simulation that assigns the causal items (ZH * num_pairs, head-major, longest first) to `grid` CTAs:
 // returns the table [rounds][grid] of item numbers (-1 = none).  Pure host code.

@@ -16,7 +16,7 @@ import torch
 from . import _lib
 
 __all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_tma_host_rows", "matmul_multi", "matmul_fused", "matmul_tma_fused", "attention", "attention_multi",
-           "attention_with_lse", "device_status"]
+           "attention_with_lse", "attention_backward", "device_status"]
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -460,9 +460,55 @@ def attention_multi(q, k, v, causal, sm_scale, out: torch.Tensor, remote_ptrs=()
     return out, M
 
 
+def attention_backward(q, k, v, o, M, d_o, causal, sm_scale):
+    """(dq, dk, dv) from what the forward saved (q, k, v, o, M: examples/fused-attn/06-fused-attention.py:269) and the
+    gradient of o.  The reference has no backward kernel; this is the consumer of its saved tensors (HEAD_DIM 128,
+    N_CTX a multiple of 128)."""
+    if q.dim() != 4 or any(t.shape != q.shape for t in (k, v, o, d_o)):
+        raise ValueError("attention_backward: q, k, v, o, d_o must be [Z, H, N_CTX, HEAD_DIM] with equal shapes")
+    if any(t.dtype != torch.bfloat16 for t in (q, k, v, o, d_o)) or M.dtype != torch.float32:
+        raise TypeError("attention_backward: bf16 q, k, v, o, d_o and fp32 M expected")
+    lib = _lib.load()
+    Z, H, N_CTX, D = q.shape
+    if tuple(M.shape) != (Z, H, N_CTX):
+        raise ValueError("attention_backward: M must be [Z, H, N_CTX]")
+    if not lib.b200k_attn_bwd_supported(D, N_CTX):
+        raise NotImplementedError(f"attention backward: no sm_100a kernel for HEAD_DIM={D}, N_CTX={N_CTX} "
+                                  "(HEAD_DIM 128, N_CTX a multiple of 128)")
+    qd, kd, vd, od, dod, Md = (_to_device(t).contiguous() for t in (q, k, v, o, d_o, M))
+    dq, dk, dv = torch.empty_like(qd), torch.empty_like(qd), torch.empty_like(qd)
+    delta = torch.empty((Z, H, N_CTX), device=qd.device, dtype=torch.float32)
+    with _on(qd.device):
+        _lib.check(lib.b200k_attn_bwd_bf16(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), od.data_ptr(), dod.data_ptr(),
+                                           Md.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(),
+                                           Z, H, N_CTX, D, 1 if causal else 0, float(sm_scale), _stream()))
+    return _like_input(dq, q), _like_input(dk, q), _like_input(dv, q)
+
+
+class _attention(torch.autograd.Function):
+    """The reference's `_attention` autograd function (examples/fused-attn/06-fused-attention.py:222-273) with the
+    backward it lacks: forward saves (q, k, v, o, M) exactly as the reference does (:269)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, warp_specialize=True):
+        o, M = attention_with_lse(q, k, v, causal, sm_scale, warp_specialize)
+        ctx.save_for_backward(q, k, v, o, M)
+        ctx.sm_scale = sm_scale
+        ctx.causal = causal
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, M = ctx.saved_tensors
+        dq, dk, dv = attention_backward(q, k, v, o, M, d_o.contiguous(), ctx.causal, ctx.sm_scale)
+        return dq, dk, dv, None, None, None
+
+
 def attention(q, k, v, causal, sm_scale, warp_specialize: bool = True) -> torch.Tensor:
     """O = softmax(Q K^T sm_scale [+ causal mask]) V.  Mirrors _attention.forward / _attention.apply,
-    examples/fused-attn/06-fused-attention.py:224-273."""
+    examples/fused-attn/06-fused-attention.py:224-273; differentiable where the backward kernels apply."""
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v)):
+        return _attention.apply(q, k, v, causal, sm_scale, warp_specialize)
     return attention_with_lse(q, k, v, causal, sm_scale, warp_specialize)[0]
 
 
