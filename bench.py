@@ -553,6 +553,15 @@ def secondary_workloads(torch, ops, gi, peaks, sampler_index):
         name = f"attention_fwd_{'causal' if causal else 'full'}"
         out[name] = {"ms": ms, "TFLOP/s": t, "frac_of_burst_peak": t / tf, "frac_of_nominal_2250": t / 2250.0}
         out[name + "_sustained"] = sustained_block(fn, fl, peaks, sampler_index, torch, probe_ms=ms)
+        # the backward on the forward's saved tensors (delta, then dK/dV, then dQ: three launches).  The figure counts
+        # the five matrix products of the algorithm (10 Z H S^2 D flop); the two kernels execute seven (S and dP twice)
+        o, m = ops.attention_with_lse(q, k, v, causal, D ** -0.5)
+        d_o = torch.randn_like(q)
+        ms = quick_ms(lambda: ops.attention_backward(q, k, v, o, m, d_o, causal, D ** -0.5), torch, rep=10)
+        t = 2.5 * fl / ms / 1e9
+        out[f"attention_bwd_{'causal' if causal else 'full'}"] = {
+            "ms": ms, "TFLOP/s": t, "frac_of_burst_peak": t / tf, "executed_TFLOP/s": t * 1.4, "launches": 3}
+        del o, m, d_o
     del q, k, v
     # the other head dimensions (same token count): 64 with twice the heads, 256 with half.  At HEAD_DIM 64 the
     # exponentials bound the kernel, not the tensor pipe: 4.29e9 exponentials per launch at 16 per clock per SM, so
