@@ -13,16 +13,20 @@
 // Two kernels, both deterministic (no atomics): one CTA per 128-key block accumulates dK and dV over the query blocks,
 // one CTA per 128-query block accumulates dQ over the key blocks; each recomputes S and dP with tcgen05 MMAs.
 //
-//   warps 0-7  two threads per row of the score tile (warps 0-3 columns 0-63, warps 4-7 columns 64-127; the backward has
-//              no row reductions, M and delta are given, so the two halves never talk): tcgen05.ld S and dP,
-//              exponentials, dS, bf16 results written back over S / dP in tensor memory; epilogue (scale, downcast,
-//              swizzled staging, TMA store), again one 64-column half each.  Two warps per scheduler instead
-//              of one: 4.48 -> 4.30 ms at Z=4, H=32, N_CTX=4096
-//   warp 8     TMA producer (the item's resident tiles; a two-stage ring of the tiles that stream)
+//   warps 0-7  one thread per row of a step's score tile; warps 0-3 take the even steps, warps 4-7 the odd ones (the
+//              backward has no row reductions, M and delta are given): tcgen05.ld S and dP, exponentials, dS, bf16
+//              results written back over S / dP in tensor memory (packed over columns the thread has already read);
+//              epilogue (scale, downcast, swizzled staging, TMA store), one 64-column half per group
+//   warp 8     TMA producer (the item's resident tiles; a four-stage ring of the half-tiles that stream)
 //   warp 9     tensor-memory owner and tcgen05.mma issuer
-// Tensor memory: dK/dV kernel S^T | dP^T | dV | dK (128 fp32 columns each, rows = keys); dQ kernel S | dP | dQ.
-// Per streamed block the chain MMA(S, dP) -> exponentials -> MMA(gradients) is serial (tensor memory holds one block),
-// only the loads run ahead.
+// Both kernels are one template.  The streamed dimension advances in steps of 64 rows (queries for dK/dV, keys for
+// dQ), so that a step's scores take 64 + 64 tensor-memory columns and two steps fit beside the accumulators:
+//   columns   0..127  step buffer 0: S | dP (64 fp32 columns each; bf16 P / dS packed over them)
+//   columns 128..255  step buffer 1
+//   columns 256..511  dV | dK   (dQ kernel: dQ | unused)
+// The issuer runs one step ahead: MMA(S, dP) of step j+1 and the gradient MMAs of step j-1 execute while the score
+// warps work on step j.  With whole 128-row blocks tensor memory held one block and the chain MMA -> exponentials ->
+// MMA was serial (4.30 ms at Z=4, H=32, N_CTX=4096 against the timings in the design notes for this version).
 #include <math.h>
 #include <string.h>
 
@@ -36,8 +40,18 @@ constexpr int BW_D = 128;
 constexpr int BW_THREADS = 320;
 constexpr int BW_SCORE_WARPS = 8;
 constexpr int BW_WARP_TMA = 8, BW_WARP_MMA = 9;
-constexpr int BW_TILE_BYTES = AT_BM * BW_D * 2;       // 32 KB: two boxes of 128 rows x 64 columns
-constexpr int BW_NSTAGE = 2;
+constexpr int BW_TILE_BYTES = AT_BM * BW_D * 2;       // 32 KB: two boxes of 128 rows x 64 columns (resident tiles)
+constexpr int BW_SUB = 64;                            // streamed rows per step
+constexpr int BW_SUB_BOX = BW_SUB * 128;              // 8 KB: 64 rows x 64 columns
+constexpr int BW_SUB_TILE = 2 * BW_SUB_BOX;           // 16 KB: 64 rows x 128 columns
+constexpr int BW_NSTAGE = 4;
+static_assert(BW_NSTAGE % 2 == 0, "the two score groups own alternate stages");
+constexpr int BW_STAGE_BYTES = 2 * BW_SUB_TILE + 1024;   // two half-tiles, then 64 M values and 64 delta values (dK/dV)
+constexpr int BW_STAGE_OFF = 2 * BW_TILE_BYTES;          // after the two resident tiles
+constexpr int BW_BAR_OFF = BW_STAGE_OFF + BW_NSTAGE * BW_STAGE_BYTES;
+constexpr int BW_NBAR = 2 + 2 * BW_NSTAGE + 2 + 2 + 2 + 1;
+constexpr int BW_SMEM_TOTAL = BW_BAR_OFF + BW_NBAR * 8 + 16 + 1024;
+static_assert(BW_SMEM_TOTAL <= 232448, "attention backward shared memory budget exceeded");
 
 struct BwdParams {
   int ZH, N_CTX, num_blk;
@@ -77,28 +91,31 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
                : "memory");
 }
 
-// Offsets (bytes) of the k-step `kk` (16 elements of the contraction) inside a 128 x 128 tile of two 64-column boxes:
-// contraction along the tile's columns (K-major operand) / along its rows (MN-major operand).
-__device__ __forceinline__ uint64_t koff_cols(int kk) {
-  return static_cast<uint64_t>(((kk >> 2) * AT_BOX_BYTES + (kk & 3) * 32) >> 4);
+// Descriptor offsets (16-byte units) of the k-step `kk` (16 elements of the contraction) inside a tile of two
+// 64-column boxes of `box_bytes` each: contraction along the tile's columns (K-major operand) / along its rows
+// (MN-major operand).
+__device__ __forceinline__ uint64_t koff_cols(int kk, int box_bytes) {
+  return static_cast<uint64_t>(((kk >> 2) * box_bytes + (kk & 3) * 32) >> 4);
 }
 __device__ __forceinline__ uint64_t koff_rows(int kk) { return static_cast<uint64_t>((kk * 2048) >> 4); }
 
-// One 128 x 128 tile: two TMA boxes.
-__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row) {
+// A tile of `rows` x 128 columns: two TMA boxes of 64 columns.
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row, int box_bytes) {
   tma_load_2d(dst, m, bar, 0, row);
-  tma_load_2d(dst + AT_BOX_BYTES, m, bar, 64, row);
+  tma_load_2d(dst + box_bytes, m, bar, 64, row);
 }
 
-// Epilogue of one accumulator: 128 rows x 128 fp32 columns of tensor memory -> x scale -> bf16 -> swizzled staging in
-// shared memory (a tile that is no longer needed); the caller issues the TMA stores of its 32 rows.
-// Tensor-memory column (relative to the fp32 score tile) of the bf16 operand's k-step kk (16 scores = 8 columns): the
-// two column halves are each packed at the start of their own 64 columns, so that no warp writes where another reads.
-__device__ __forceinline__ constexpr uint32_t bf16_col(int kk) { return kk < 4 ? kk * 8 : 64 + (kk - 4) * 8; }
+// Tensor-memory column (relative to a step's fp32 score tile of 64 columns) of the bf16 operand's k-step kk (16 scores
+// = 8 columns): each thread packs its 32 scores at the start of its own 32 columns, so no warp writes where another
+// still reads.
+__device__ __forceinline__ constexpr uint32_t bf16_col(int kk) { return (kk >> 1) * 32 + (kk & 1) * 8; }
 
+// Epilogue of one accumulator: 128 rows x 128 fp32 columns of tensor memory -> x scale -> bf16 -> swizzled staging in
+// shared memory (a resident tile that is no longer needed); each thread takes the 64-column box `half` of its row and
+// the caller issues the TMA stores of its warp's 32 rows.
 __device__ __forceinline__ void store_acc(uint32_t t_acc, float scale, uint8_t* stage, int r, int half) {
 #pragma unroll 1
-  for (int c4 = 2 * half; c4 < 2 * half + 2; ++c4) {   // this thread's 64 columns = one 64-column box
+  for (int c4 = 2 * half; c4 < 2 * half + 2; ++c4) {
     uint32_t o[32];
     tmem_ld_x32(t_acc + c4 * 32, o);
     tmem_wait_ld();
@@ -116,283 +133,118 @@ __device__ __forceinline__ void store_acc(uint32_t t_acc, float scale, uint8_t* 
   }
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// dK and dV: one item = (batch*head, key block n); the query blocks m stream (m >= n when causal)
-// ---------------------------------------------------------------------------------------------------------------
-constexpr int KV_STAGE_BYTES = 2 * BW_TILE_BYTES + 1024;          // Q tile, dO tile, 128 M values, 128 delta values
-constexpr int KV_RES_OFF = 0;                                     // K tile, V tile (resident per item)
-constexpr int KV_STAGE_OFF = 2 * BW_TILE_BYTES;
-constexpr int KV_BAR_OFF = KV_STAGE_OFF + BW_NSTAGE * KV_STAGE_BYTES;
-constexpr int KV_NBAR = 2 + 2 * BW_NSTAGE + 4;
-constexpr int KV_SMEM_TOTAL = KV_BAR_OFF + KV_NBAR * 8 + 16 + 1024;
-static_assert(KV_SMEM_TOTAL <= 232448, "attention backward (dK/dV) shared memory budget exceeded");
-
-__global__ void __launch_bounds__(BW_THREADS, 1)
-attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                             const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                             const __grid_constant__ CUtensorMap tmap_dk, const __grid_constant__ CUtensorMap tmap_dv,
-                             const BwdParams p) {
-  constexpr uint32_t IDESC_SS = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);   // both operands K-major
-  constexpr uint32_t IDESC_TS = umma_idesc_bf16_f32(AT_BM, BW_D, 0, 1);    // A in tensor memory, B MN-major
-  constexpr uint32_t C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 384;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_k = smem + KV_RES_OFF;
-  uint8_t* smem_v = smem_k + BW_TILE_BYTES;
-  uint8_t* smem_stage = smem + KV_STAGE_OFF;
-  uint64_t* res_full = reinterpret_cast<uint64_t*>(smem + KV_BAR_OFF);   // K and V tiles have arrived
-  uint64_t* res_empty = res_full + 1;                                    // ... may be overwritten (4 warps)
-  uint64_t* st_full = res_empty + 1;                                     // [stage] Q, dO, M, delta have arrived
-  uint64_t* st_empty = st_full + BW_NSTAGE;                              // [stage] released by the MMA issuer
-  uint64_t* x_full = st_empty + BW_NSTAGE;                               // S^T and dP^T are in tensor memory
-  uint64_t* p_ready = x_full + 1;                                        // P^T and dS^T written (4 warps)
-  uint64_t* acc_full = p_ready + 1;                                      // dV and dK complete
-  uint64_t* acc_empty = acc_full + 1;                                    // ... read out (4 warps)
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_empty + 1);
-  uint32_t* abort_smem = tmem_ptr_smem + 1;
-
-  const int warp_idx = threadIdx.x >> 5;
-  const uint32_t lane = lane_id();
-  WaitCtx ctx{abort_smem, p.status};
-
-  if (threadIdx.x == 0) {
-    mbar_init(res_full, 1);
-    mbar_init(res_empty, BW_SCORE_WARPS);
-    for (int s = 0; s < BW_NSTAGE; ++s) {
-      mbar_init(&st_full[s], 1);
-      mbar_init(&st_empty[s], 1);
+// The score work of one thread for one step: its row's 64 fp32 scores S and 64 values dP in the step buffer `t_buf`
+// (S at columns 0..63, dP at 64..127) become bf16 dS (and P for dK/dV), packed over the first 16 columns of every 32
+// just read.  Sixteen columns at a time, the next sixteen in flight meanwhile; pairs of scores go through the packed
+// fp32 instructions (each lane rounds like the scalar form), because the issue slots beside the exponentials are
+// what bounds this loop (about 9 cycles per exponential with two other instructions, 14 with four).
+//   dK/dV (rows = keys): M and delta differ per column and come from shared memory: p = exp2(-(M - s * qk_scale)),
+//                        dS = p * (dP - delta); masked (diagonal block) where query < key
+//   dQ (rows = queries): M and delta are this thread's: p = exp2(s * qk_scale - M); masked where key > query
+template <bool DKDV, bool MASKED>
+__device__ __forceinline__ void score_step(uint32_t t_buf, const float* vec, float qk_scale, float m_i, float d_i, int col0,
+                                           int r) {
+  const uint64_t scale2 = DKDV ? pack_f32x2(-qk_scale, -qk_scale) : pack_f32x2(qk_scale, qk_scale);
+  const uint64_t negm2 = pack_f32x2(-m_i, -m_i), negd2 = pack_f32x2(-d_i, -d_i);
+  const uint64_t minus1 = pack_f32x2(-1.0f, -1.0f);
+  uint32_t s[2][16], d[2][16];
+  uint32_t pp[16], ds[16];
+  tmem_ld_x16(t_buf, s[0]);
+  tmem_ld_x16(t_buf + 64, d[0]);
+  tmem_wait_ld();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (k + 1 < 4) {
+      tmem_ld_x16(t_buf + (k + 1) * 16, s[(k + 1) & 1]);
+      tmem_ld_x16(t_buf + 64 + (k + 1) * 16, d[(k + 1) & 1]);
     }
-    mbar_init(x_full, 1);
-    mbar_init(p_ready, BW_SCORE_WARPS);
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, BW_SCORE_WARPS);
-    *abort_smem = 0;
-    fence_mbar_init();
-    prefetch_tmap(&tmap_q);
-    prefetch_tmap(&tmap_k);
-    prefetch_tmap(&tmap_v);
-    prefetch_tmap(&tmap_do);
-  }
-  if (warp_idx == BW_WARP_MMA) {
-    tmem_alloc(tmem_ptr_smem, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_ptr_smem;
-
-  if (warp_idx == BW_WARP_TMA) {
-    // ------------------------------------------------------------------ TMA producer
-    int stage = 0;
-    uint32_t stage_phase = 0, items = 0;
-    bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      const int hz = item / p.num_blk, n = item - hz * p.num_blk;
-      const int row_base = hz * p.N_CTX;
-      ok = mbar_wait(res_empty, (items & 1u) ^ 1u, ctx, 80);
-      if (!ok) break;
-      if (lane == 0) {
-        mbar_expect_tx(res_full, 2 * BW_TILE_BYTES);
-        load_tile(smem_k, &tmap_k, res_full, row_base + n * AT_BN);
-        load_tile(smem_v, &tmap_v, res_full, row_base + n * AT_BN);
-      }
-      __syncwarp();
-      for (int m = p.causal ? n : 0; ok && m < p.num_blk; ++m) {
-        ok = mbar_wait(&st_empty[stage], stage_phase ^ 1u, ctx, 81);
-        if (!ok) break;
-        if (lane == 0) {
-          uint8_t* dst = smem_stage + stage * KV_STAGE_BYTES;
-          mbar_expect_tx(&st_full[stage], 2 * BW_TILE_BYTES + 1024);
-          load_tile(dst, &tmap_q, &st_full[stage], row_base + m * AT_BM);
-          load_tile(dst + BW_TILE_BYTES, &tmap_do, &st_full[stage], row_base + m * AT_BM);
-          bulk_load_1d(dst + 2 * BW_TILE_BYTES, p.lse2 + row_base + m * AT_BM, 512, &st_full[stage]);
-          bulk_load_1d(dst + 2 * BW_TILE_BYTES + 512, p.delta + row_base + m * AT_BM, 512, &st_full[stage]);
+    const uint32_t(&sk)[16] = s[k & 1];
+    const uint32_t(&dk)[16] = d[k & 1];
+#pragma unroll
+    for (int c = 0; c < 16; c += 2) {
+      const uint64_t s2 = pack_f32x2(__uint_as_float(sk[c]), __uint_as_float(sk[c + 1]));
+      const uint64_t d2 = pack_f32x2(__uint_as_float(dk[c]), __uint_as_float(dk[c + 1]));
+      float x0, x1, p0, p1;
+      uint64_t t2;
+      if (DKDV) {
+        const float2 m2 = *reinterpret_cast<const float2*>(vec + k * 16 + c);
+        const float2 dl2 = *reinterpret_cast<const float2*>(vec + 64 + k * 16 + c);
+        unpack_f32x2(fma_f32x2(s2, scale2, pack_f32x2(m2.x, m2.y)), x0, x1);     // M - s * qk_scale
+        p0 = ex2_approx(-x0);
+        p1 = ex2_approx(-x1);
+        t2 = fma_f32x2(pack_f32x2(dl2.x, dl2.y), minus1, d2);                     // dP - delta
+        if (MASKED) {
+          if (col0 + k * 16 + c < r) p0 = 0.f;                                    // query index < key index
+          if (col0 + k * 16 + c + 1 < r) p1 = 0.f;
         }
-        __syncwarp();
-        if (++stage == BW_NSTAGE) { stage = 0; stage_phase ^= 1u; }
+        pp[(k & 1) * 8 + c / 2] = pack_bf16x2(p0, p1);
+      } else {
+        unpack_f32x2(fma_f32x2(s2, scale2, negm2), x0, x1);
+        p0 = ex2_approx(x0);
+        p1 = ex2_approx(x1);
+        t2 = add_f32x2(d2, negd2);
+        if (MASKED) {
+          if (col0 + k * 16 + c > r) p0 = 0.f;                                    // key index > query index
+          if (col0 + k * 16 + c + 1 > r) p1 = 0.f;
+        }
+      }
+      float y0, y1;
+      unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), t2), y0, y1);
+      ds[(k & 1) * 8 + c / 2] = pack_bf16x2(y0, y1);
+    }
+    if (k & 1) {   // 32 scores done: 16 columns of bf16 over the start of the 32 columns they came from
+      if (DKDV) {
+        tmem_st_x16(t_buf + (k >> 1) * 32, pp);
+        tmem_st_x16(t_buf + 64 + (k >> 1) * 32, ds);
+      } else {
+        tmem_st_x16(t_buf + (k >> 1) * 32, ds);
       }
     }
-  } else if (warp_idx == BW_WARP_MMA) {
-    // ------------------------------------------------------------------ MMA issuer
-    int stage = 0;
-    uint32_t stage_phase = 0, items = 0, blocks = 0;
-    bool ok = true;
-    const uint64_t k_desc = umma_smem_desc_sw128(smem_u32(smem_k), 16, 1024);
-    const uint64_t v_desc = umma_smem_desc_sw128(smem_u32(smem_v), 16, 1024);
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      const int hz = item / p.num_blk, n = item - hz * p.num_blk;
-      ok = mbar_wait(res_full, items & 1u, ctx, 82);
-      if (!ok) break;
-      bool first = true;
-      for (int m = p.causal ? n : 0; ok && m < p.num_blk; ++m, ++blocks) {
-        ok = mbar_wait(&st_full[stage], stage_phase, ctx, 83);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(smem_stage + stage * KV_STAGE_BYTES);
-        const uint32_t do_addr = q_addr + BW_TILE_BYTES;
-        if (lane == 0) {
-          // S^T = K Q^T and dP^T = V dO^T: rows = keys, columns = queries, contraction over the head dimension
-          const uint64_t qk = umma_smem_desc_sw128(q_addr, 16, 1024), dok = umma_smem_desc_sw128(do_addr, 16, 1024);
-#pragma unroll
-          for (int kk = 0; kk < BW_D / 16; ++kk)
-            umma_ss(tmem_base + C_ST, k_desc + koff_cols(kk), qk + koff_cols(kk), IDESC_SS, kk > 0 ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < BW_D / 16; ++kk)
-            umma_ss(tmem_base + C_DPT, v_desc + koff_cols(kk), dok + koff_cols(kk), IDESC_SS, kk > 0 ? 1u : 0u);
-          umma_commit(x_full);
-        }
-        __syncwarp();
-        ok = mbar_wait(p_ready, blocks & 1u, ctx, 84);
-        if (!ok) break;
-        if (first) {   // the previous item's dV / dK must have left tensor memory before they are overwritten
-          ok = mbar_wait(acc_empty, (items & 1u) ^ 1u, ctx, 85);
-          if (!ok) break;
-        }
-        tc_fence_after();
-        if (lane == 0) {
-          // dV += P^T dO and dK += dS^T Q: A from tensor memory (bf16, 8 columns per k-step), contraction over the queries
-          const uint64_t qn = umma_smem_desc_sw128(q_addr, AT_BOX_BYTES, 1024);
-          const uint64_t don = umma_smem_desc_sw128(do_addr, AT_BOX_BYTES, 1024);
-#pragma unroll
-          for (int kk = 0; kk < AT_BM / 16; ++kk)
-            umma_ts(tmem_base + C_DV, tmem_base + C_ST + bf16_col(kk), don + koff_rows(kk), IDESC_TS, (!first || kk > 0) ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < AT_BM / 16; ++kk)
-            umma_ts(tmem_base + C_DK, tmem_base + C_DPT + bf16_col(kk), qn + koff_rows(kk), IDESC_TS, (!first || kk > 0) ? 1u : 0u);
-          umma_commit(&st_empty[stage]);
-          if (m == p.num_blk - 1) umma_commit(acc_full);
-        }
-        __syncwarp();
-        first = false;
-        if (++stage == BW_NSTAGE) { stage = 0; stage_phase ^= 1u; }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------ score rows (warps 0..7): thread = (key, column half)
-    const int q = warp_idx & 3;          // tensor-memory lane quarter
-    const int half = warp_idx >> 2;      // columns [64 * half, 64 * half + 64)
-    const int r = q * 32 + static_cast<int>(lane);
-    const uint32_t lane_field = static_cast<uint32_t>(q * 32) << 16;
-    const uint32_t t_st = tmem_base + lane_field + C_ST, t_dpt = tmem_base + lane_field + C_DPT;
-    int stage = 0;
-    uint32_t stage_phase = 0, items = 0, blocks = 0;
-    bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      const int hz = item / p.num_blk, n = item - hz * p.num_blk;
-      for (int m = p.causal ? n : 0; ok && m < p.num_blk; ++m, ++blocks) {
-        // the stage's M and delta vectors are read from shared memory below: observe their arrival directly
-        ok = mbar_wait(&st_full[stage], stage_phase, ctx, 88);
-        if (!ok) break;
-        ok = mbar_wait(x_full, blocks & 1u, ctx, 86);
-        if (!ok) break;
-        tc_fence_after();
-        const float* mv = reinterpret_cast<const float*>(smem_stage + stage * KV_STAGE_BYTES + 2 * BW_TILE_BYTES);
-        const float* dv = mv + 128;
-        const bool diag = p.causal && m == n;
-#pragma unroll 1
-        for (int c4 = 2 * half; c4 < 2 * half + 2; ++c4) {
-          uint32_t s[32], d[32];
-          tmem_ld_x32(t_st + c4 * 32, s);
-          tmem_ld_x32(t_dpt + c4 * 32, d);
-          tmem_wait_ld();
-          uint32_t pp[16], ds[16];
-#pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            const float4 m4 = *reinterpret_cast<const float4*>(mv + c4 * 32 + c);
-            const float4 d4 = *reinterpret_cast<const float4*>(dv + c4 * 32 + c);
-            const float mm[4] = {m4.x, m4.y, m4.z, m4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
-            float pv[4], dsv[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float pe = ex2_approx(fmaf(__uint_as_float(s[c + e]), p.qk_scale, -mm[e]));
-              if (diag && c4 * 32 + c + e < r) pe = 0.f;          // query index < key index
-              pv[e] = pe;
-              dsv[e] = pe * (__uint_as_float(d[c + e]) - dd[e]);
-            }
-            pp[c / 2] = pack_bf16x2(pv[0], pv[1]);
-            pp[c / 2 + 1] = pack_bf16x2(pv[2], pv[3]);
-            ds[c / 2] = pack_bf16x2(dsv[0], dsv[1]);
-            ds[c / 2 + 1] = pack_bf16x2(dsv[2], dsv[3]);
-          }
-          // the bf16 results land in columns this thread has already read (16 columns per 32 scores, packed from
-          // the start of the thread's own 64-column half: the other half's warps run at their own pace)
-          tmem_st_x16(t_st + bf16_col(c4 * 2), pp);
-          tmem_st_x16(t_dpt + bf16_col(c4 * 2), ds);
-        }
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(p_ready);
-        if (++stage == BW_NSTAGE) { stage = 0; stage_phase ^= 1u; }
-      }
-      if (!ok) break;
-      // ---- epilogue: dV and sm_scale * dK -> bf16 -> staging in the K / V tiles (no longer needed) -> TMA store
-      ok = mbar_wait(acc_full, items & 1u, ctx, 87);
-      if (!ok) break;
-      tc_fence_after();
-      store_acc(tmem_base + lane_field + C_DV, 1.0f, smem_k, r, half);
-      store_acc(tmem_base + lane_field + C_DK, p.sm_scale, smem_v, r, half);
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(acc_empty);
-        const int y = hz * p.N_CTX + n * AT_BN + q * 32;
-        tma_store_2d(&tmap_dv, smem_k + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
-        tma_store_2d(&tmap_dk, smem_v + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
-        tma_store_commit();
-        tma_store_wait_read<0>();
-        mbar_arrive(res_empty);
-      }
-      __syncwarp();
-    }
-    if (lane == 0) tma_store_wait_all<0>();
-    __syncwarp();
-  }
-
-  // ------------------------------------------------------------------ teardown
-  drain_after_abort(abort_smem);
-  tc_fence_before();
-  __syncthreads();
-  if (warp_idx == BW_WARP_MMA) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (k + 1 < 4) tmem_wait_ld();
   }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// dQ: one item = (batch*head, query block m); the key blocks n stream (n <= m when causal)
+// DKDV = true:  one item = (batch*head, key block n); resident K, V; the queries stream (blocks m >= n when causal):
+//               S^T = K Qs^T, dP^T = V dOs^T (rows = keys), dV += P^T dOs, dK += dS^T Qs.
+// DKDV = false: one item = (batch*head, query block m); resident Q, dO; the keys stream (blocks n <= m when causal):
+//               S = Q Ks^T, dP = dO Vs^T (rows = queries), dQ += dS Ks.
+// "res0/res1" are the resident pair, "str0/str1" the streamed pair (the factor of res0 / res1 in the score products),
+// "out0/out1" the results (dV, dK or dQ, -).
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int DQ_STAGE_BYTES = 2 * BW_TILE_BYTES;                 // K tile, V tile
-constexpr int DQ_STAGE_OFF = 2 * BW_TILE_BYTES;                   // after the resident Q and dO tiles
-constexpr int DQ_BAR_OFF = DQ_STAGE_OFF + BW_NSTAGE * DQ_STAGE_BYTES;
-constexpr int DQ_SMEM_TOTAL = DQ_BAR_OFF + KV_NBAR * 8 + 16 + 1024;
-static_assert(DQ_SMEM_TOTAL <= 232448, "attention backward (dQ) shared memory budget exceeded");
-
+template <bool DKDV>
 __global__ void __launch_bounds__(BW_THREADS, 1)
-attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                           const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                           const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
-  constexpr uint32_t IDESC_SS = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);
-  constexpr uint32_t IDESC_TS = umma_idesc_bf16_f32(AT_BM, BW_D, 0, 1);
-  constexpr uint32_t C_S = 0, C_DP = 128, C_DQ = 256;
+attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_res0, const __grid_constant__ CUtensorMap tmap_res1,
+                        const __grid_constant__ CUtensorMap tmap_str0, const __grid_constant__ CUtensorMap tmap_str1,
+                        const __grid_constant__ CUtensorMap tmap_out0, const __grid_constant__ CUtensorMap tmap_out1,
+                        const BwdParams p) {
+  constexpr uint32_t IDESC_X = umma_idesc_bf16_f32(AT_BM, BW_SUB, 0, 0);   // scores: both operands K-major, N = 64
+  constexpr uint32_t IDESC_G = umma_idesc_bf16_f32(AT_BM, BW_D, 0, 1);     // gradients: A in tensor memory, B MN-major
+  constexpr uint32_t C_ACC0 = 256, C_ACC1 = 384;
+  // dQ has one accumulator, so its resident tiles (Q, dO) fit in tensor memory as bf16 A operands (64 columns each):
+  // the score MMAs then read only the streamed half-tile from shared memory (32 KB per step instead of 96 KB; shared
+  // memory bandwidth, 128 bytes per clock, is what bounds these MMAs at N = 64).  dK/dV has no columns to spare.
+  constexpr bool RES_TMEM = !DKDV;
+  constexpr uint32_t C_RES0 = 384, C_RES1 = 448;
+  constexpr uint32_t STAGE_TX = 2 * BW_SUB_TILE + (DKDV ? 512 : 0);
+  // wait sites: 80.. for dK/dV, 90.. for dQ
+  constexpr uint32_t SITE = DKDV ? 80 : 90;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_q = smem;
-  uint8_t* smem_do = smem + BW_TILE_BYTES;
-  uint8_t* smem_stage = smem + DQ_STAGE_OFF;
-  uint64_t* res_full = reinterpret_cast<uint64_t*>(smem + DQ_BAR_OFF);
-  uint64_t* res_empty = res_full + 1;
-  uint64_t* st_full = res_empty + 1;
-  uint64_t* st_empty = st_full + BW_NSTAGE;
-  uint64_t* x_full = st_empty + BW_NSTAGE;
-  uint64_t* p_ready = x_full + 1;
-  uint64_t* acc_full = p_ready + 1;
-  uint64_t* acc_empty = acc_full + 1;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  uint8_t* smem_res0 = smem;
+  uint8_t* smem_res1 = smem + BW_TILE_BYTES;
+  uint8_t* smem_stage = smem + BW_STAGE_OFF;
+  uint64_t* res_full = reinterpret_cast<uint64_t*>(smem + BW_BAR_OFF);   // resident tiles have arrived
+  uint64_t* res_empty = res_full + 1;                                    // ... may be overwritten (8 warps)
+  uint64_t* st_full = res_empty + 1;                                     // [stage] the step's half-tiles have arrived
+  uint64_t* st_empty = st_full + BW_NSTAGE;                              // [stage] released by the MMA issuer
+  uint64_t* x_full = st_empty + BW_NSTAGE;                               // [buffer] S and dP are in tensor memory
+  uint64_t* p_ready = x_full + 2;                                        // [buffer] bf16 P / dS written (4 warps)
+  uint64_t* acc_full = p_ready + 2;                                      // accumulators complete
+  uint64_t* acc_empty = acc_full + 1;                                    // ... read out (8 warps)
+  uint64_t* res_ready = acc_empty + 1;                                   // resident tiles copied to tensor memory (8 warps)
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(res_ready + 1);
   uint32_t* abort_smem = tmem_ptr_smem + 1;
 
   const int warp_idx = threadIdx.x >> 5;
@@ -406,16 +258,19 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       mbar_init(&st_full[s], 1);
       mbar_init(&st_empty[s], 1);
     }
-    mbar_init(x_full, 1);
-    mbar_init(p_ready, BW_SCORE_WARPS);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&x_full[b], 1);
+      mbar_init(&p_ready[b], BW_SCORE_WARPS / 2);
+    }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, BW_SCORE_WARPS);
+    mbar_init(res_ready, BW_SCORE_WARPS);
     *abort_smem = 0;
     fence_mbar_init();
-    prefetch_tmap(&tmap_q);
-    prefetch_tmap(&tmap_k);
-    prefetch_tmap(&tmap_v);
-    prefetch_tmap(&tmap_do);
+    prefetch_tmap(&tmap_res0);
+    prefetch_tmap(&tmap_res1);
+    prefetch_tmap(&tmap_str0);
+    prefetch_tmap(&tmap_str1);
   }
   if (warp_idx == BW_WARP_MMA) {
     tmem_alloc(tmem_ptr_smem, 512);
@@ -426,11 +281,19 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  // causal items take m + 1 blocks: hand out the long ones first
-  auto item_block = [&](int item, int& hz, int& m) {
+  // item -> (batch*head, resident block, range of streamed blocks).  Causal items differ in length: the long ones
+  // are handed out first (dK/dV: small n; dQ: large m).
+  auto item_range = [&](int item, int& hz, int& blk, int& s_begin, int& s_end) {
     hz = item / p.num_blk;
-    m = item - hz * p.num_blk;
-    if (p.causal) m = p.num_blk - 1 - m;
+    blk = item - hz * p.num_blk;
+    if (DKDV) {
+      s_begin = p.causal ? blk : 0;
+      s_end = p.num_blk;
+    } else {
+      if (p.causal) blk = p.num_blk - 1 - blk;
+      s_begin = 0;
+      s_end = p.causal ? blk + 1 : p.num_blk;
+    }
   };
 
   if (warp_idx == BW_WARP_TMA) {
@@ -439,26 +302,30 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     uint32_t stage_phase = 0, items = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      int hz, m;
-      item_block(item, hz, m);
+      int hz, blk, s_begin, s_end;
+      item_range(item, hz, blk, s_begin, s_end);
       const int row_base = hz * p.N_CTX;
-      ok = mbar_wait(res_empty, (items & 1u) ^ 1u, ctx, 90);
+      ok = mbar_wait(res_empty, (items & 1u) ^ 1u, ctx, SITE + 0);
       if (!ok) break;
       if (lane == 0) {
         mbar_expect_tx(res_full, 2 * BW_TILE_BYTES);
-        load_tile(smem_q, &tmap_q, res_full, row_base + m * AT_BM);
-        load_tile(smem_do, &tmap_do, res_full, row_base + m * AT_BM);
+        load_tile(smem_res0, &tmap_res0, res_full, row_base + blk * AT_BM, AT_BOX_BYTES);
+        load_tile(smem_res1, &tmap_res1, res_full, row_base + blk * AT_BM, AT_BOX_BYTES);
       }
       __syncwarp();
-      const int n_end = p.causal ? m + 1 : p.num_blk;
-      for (int n = 0; ok && n < n_end; ++n) {
-        ok = mbar_wait(&st_empty[stage], stage_phase ^ 1u, ctx, 91);
+      for (int step = 2 * s_begin; ok && step < 2 * s_end; ++step) {
+        ok = mbar_wait(&st_empty[stage], stage_phase ^ 1u, ctx, SITE + 1);
         if (!ok) break;
         if (lane == 0) {
-          uint8_t* dst = smem_stage + stage * DQ_STAGE_BYTES;
-          mbar_expect_tx(&st_full[stage], 2 * BW_TILE_BYTES);
-          load_tile(dst, &tmap_k, &st_full[stage], row_base + n * AT_BN);
-          load_tile(dst + BW_TILE_BYTES, &tmap_v, &st_full[stage], row_base + n * AT_BN);
+          uint8_t* dst = smem_stage + stage * BW_STAGE_BYTES;
+          const int row = row_base + step * BW_SUB;
+          mbar_expect_tx(&st_full[stage], STAGE_TX);
+          load_tile(dst, &tmap_str0, &st_full[stage], row, BW_SUB_BOX);
+          load_tile(dst + BW_SUB_TILE, &tmap_str1, &st_full[stage], row, BW_SUB_BOX);
+          if (DKDV) {
+            bulk_load_1d(dst + 2 * BW_SUB_TILE, p.lse2 + row, 256, &st_full[stage]);
+            bulk_load_1d(dst + 2 * BW_SUB_TILE + 256, p.delta + row, 256, &st_full[stage]);
+          }
         }
         __syncwarp();
         if (++stage == BW_NSTAGE) { stage = 0; stage_phase ^= 1u; }
@@ -466,110 +333,165 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     }
   } else if (warp_idx == BW_WARP_MMA) {
     // ------------------------------------------------------------------ MMA issuer
-    int stage = 0;
-    uint32_t stage_phase = 0, items = 0, blocks = 0;
+    int xs = 0, gs = 0;                 // ring positions of the next score step / the next gradient step
+    uint32_t xs_phase = 0, items = 0, blocks = 0;
     bool ok = true;
-    const uint64_t q_desc = umma_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
-    const uint64_t do_desc = umma_smem_desc_sw128(smem_u32(smem_do), 16, 1024);
+    const uint64_t r0_desc = umma_smem_desc_sw128(smem_u32(smem_res0), 16, 1024);
+    const uint64_t r1_desc = umma_smem_desc_sw128(smem_u32(smem_res1), 16, 1024);
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      int hz, m;
-      item_block(item, hz, m);
-      ok = mbar_wait(res_full, items & 1u, ctx, 92);
+      int hz, blk, s_begin, s_end;
+      item_range(item, hz, blk, s_begin, s_end);
+      ok = mbar_wait(RES_TMEM ? res_ready : res_full, items & 1u, ctx, SITE + 2);
       if (!ok) break;
-      const int n_end = p.causal ? m + 1 : p.num_blk;
-      for (int n = 0; ok && n < n_end; ++n, ++blocks) {
-        ok = mbar_wait(&st_full[stage], stage_phase, ctx, 93);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem_stage + stage * DQ_STAGE_BYTES);
-        const uint32_t v_addr = k_addr + BW_TILE_BYTES;
-        if (lane == 0) {
-          // S = Q K^T and dP = dO V^T: rows = queries, columns = keys
-          const uint64_t kk_desc = umma_smem_desc_sw128(k_addr, 16, 1024), vk_desc = umma_smem_desc_sw128(v_addr, 16, 1024);
-#pragma unroll
-          for (int kk = 0; kk < BW_D / 16; ++kk)
-            umma_ss(tmem_base + C_S, q_desc + koff_cols(kk), kk_desc + koff_cols(kk), IDESC_SS, kk > 0 ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < BW_D / 16; ++kk)
-            umma_ss(tmem_base + C_DP, do_desc + koff_cols(kk), vk_desc + koff_cols(kk), IDESC_SS, kk > 0 ? 1u : 0u);
-          umma_commit(x_full);
-        }
-        __syncwarp();
-        ok = mbar_wait(p_ready, blocks & 1u, ctx, 94);
-        if (!ok) break;
-        if (n == 0) {
-          ok = mbar_wait(acc_empty, (items & 1u) ^ 1u, ctx, 95);
+      tc_fence_after();
+      const int total = 2 * (s_end - s_begin);
+      for (int j = 0; ok && j <= total; ++j) {
+        if (j < total) {
+          // scores of step j into buffer j & 1.  Its previous user (step j - 2) has been read by the score warps
+          // (p_ready was observed) and its gradient MMAs were issued before these; the tensor pipe runs in order
+          ok = mbar_wait(&st_full[xs], xs_phase, ctx, SITE + 3);
           if (!ok) break;
-        }
-        tc_fence_after();
-        if (lane == 0) {
-          // dQ += dS K: A = dS (bf16 in tensor memory over S), contraction over the keys
-          const uint64_t kn_desc = umma_smem_desc_sw128(k_addr, AT_BOX_BYTES, 1024);
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a0 = smem_u32(smem_stage + xs * BW_STAGE_BYTES);
+            const uint64_t s0 = umma_smem_desc_sw128(a0, 16, 1024), s1 = umma_smem_desc_sw128(a0 + BW_SUB_TILE, 16, 1024);
+            const uint32_t t = tmem_base + (j & 1) * 128;
+            if (RES_TMEM) {
 #pragma unroll
-          for (int kk = 0; kk < AT_BN / 16; ++kk)
-            umma_ts(tmem_base + C_DQ, tmem_base + C_S + bf16_col(kk), kn_desc + koff_rows(kk), IDESC_TS, (n > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(&st_empty[stage]);
-          if (n == n_end - 1) umma_commit(acc_full);
+              for (int kk = 0; kk < BW_D / 16; ++kk)
+                umma_ts(t, tmem_base + C_RES0 + kk * 8, s0 + koff_cols(kk, BW_SUB_BOX), IDESC_X, kk > 0 ? 1u : 0u);
+#pragma unroll
+              for (int kk = 0; kk < BW_D / 16; ++kk)
+                umma_ts(t + 64, tmem_base + C_RES1 + kk * 8, s1 + koff_cols(kk, BW_SUB_BOX), IDESC_X, kk > 0 ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < BW_D / 16; ++kk)
+                umma_ss(t, r0_desc + koff_cols(kk, AT_BOX_BYTES), s0 + koff_cols(kk, BW_SUB_BOX), IDESC_X, kk > 0 ? 1u : 0u);
+#pragma unroll
+              for (int kk = 0; kk < BW_D / 16; ++kk)
+                umma_ss(t + 64, r1_desc + koff_cols(kk, AT_BOX_BYTES), s1 + koff_cols(kk, BW_SUB_BOX), IDESC_X, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&x_full[j & 1]);
+          }
+          __syncwarp();
+          if (++xs == BW_NSTAGE) { xs = 0; xs_phase ^= 1u; }
         }
-        __syncwarp();
-        if (++stage == BW_NSTAGE) { stage = 0; stage_phase ^= 1u; }
+        if (j > 0) {
+          // gradients of step j - 1: A = bf16 P / dS in tensor memory (8 columns per k-step of 16 streamed rows)
+          const int jj = j - 1;
+          ok = mbar_wait(&p_ready[jj & 1], (blocks + (jj >> 1)) & 1u, ctx, SITE + 4);
+          if (!ok) break;
+          if (jj == 0) {   // the previous item's accumulators must have left tensor memory before they are overwritten
+            ok = mbar_wait(acc_empty, (items & 1u) ^ 1u, ctx, SITE + 5);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a0 = smem_u32(smem_stage + gs * BW_STAGE_BYTES);
+            const uint64_t n0 = umma_smem_desc_sw128(a0, BW_SUB_BOX, 1024);
+            const uint64_t n1 = umma_smem_desc_sw128(a0 + BW_SUB_TILE, BW_SUB_BOX, 1024);
+            const uint32_t t = tmem_base + (jj & 1) * 128;
+            if (DKDV) {
+#pragma unroll
+              for (int kk = 0; kk < BW_SUB / 16; ++kk)   // dV += P^T dOs
+                umma_ts(tmem_base + C_ACC0, t + bf16_col(kk), n1 + koff_rows(kk), IDESC_G, (jj > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+              for (int kk = 0; kk < BW_SUB / 16; ++kk)   // dK += dS^T Qs
+                umma_ts(tmem_base + C_ACC1, t + 64 + bf16_col(kk), n0 + koff_rows(kk), IDESC_G, (jj > 0 || kk > 0) ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < BW_SUB / 16; ++kk)   // dQ += dS Ks
+                umma_ts(tmem_base + C_ACC0, t + bf16_col(kk), n0 + koff_rows(kk), IDESC_G, (jj > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(&st_empty[gs]);
+            if (jj == total - 1) umma_commit(acc_full);
+          }
+          __syncwarp();
+          if (++gs == BW_NSTAGE) gs = 0;
+        }
       }
+      blocks += static_cast<uint32_t>(s_end - s_begin);
     }
   } else {
-    // ------------------------------------------------------------------ score rows (warps 0..7): thread = (query, column half)
+    // ------------------------------------------------------------------ score rows (warps 0..7)
+    // warps 0-3 take the even steps (buffer 0), warps 4-7 the odd ones (buffer 1): the two warps that share a scheduler
+    // are half a period apart, so one computes while the other waits for its MMAs, loads and stores
     const int q = warp_idx & 3;          // tensor-memory lane quarter
-    const int half = warp_idx >> 2;      // columns [64 * half, 64 * half + 64)
+    const int half = warp_idx >> 2;      // step buffer; in the epilogue the 64-column box
     const int r = q * 32 + static_cast<int>(lane);
     const uint32_t lane_field = static_cast<uint32_t>(q * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_field + C_S, t_dp = tmem_base + lane_field + C_DP;
-    uint32_t items = 0, blocks = 0;
+    const uint32_t t_buf = tmem_base + lane_field + half * 128;
+    int stage = half;                    // ring position of this group's next step (steps alternate between the groups)
+    uint32_t stage_phase = 0, items = 0, blocks = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      int hz, m;
-      item_block(item, hz, m);
-      const int64_t my_row = static_cast<int64_t>(hz) * p.N_CTX + m * AT_BM + r;
-      const float m_i = __ldg(p.lse2 + my_row), d_i = __ldg(p.delta + my_row);
-      const int n_end = p.causal ? m + 1 : p.num_blk;
-      for (int n = 0; ok && n < n_end; ++n, ++blocks) {
-        ok = mbar_wait(x_full, blocks & 1u, ctx, 96);
+      int hz, blk, s_begin, s_end;
+      item_range(item, hz, blk, s_begin, s_end);
+      float m_i = 0.f, d_i = 0.f;
+      if (!DKDV) {
+        const int64_t my_row = static_cast<int64_t>(hz) * p.N_CTX + blk * AT_BM + r;
+        m_i = __ldg(p.lse2 + my_row);
+        d_i = __ldg(p.delta + my_row);
+      }
+      if (RES_TMEM) {
+        // group 0 copies Q, group 1 dO: each thread its row, 128 bf16 -> 64 columns (two values per column, the layout
+        // of an MMA A operand in tensor memory).  The previous item's MMAs have all completed (acc_full was observed)
+        ok = mbar_wait(res_full, items & 1u, ctx, SITE + 9);
         if (!ok) break;
-        tc_fence_after();
-        const bool diag = p.causal && n == m;
-#pragma unroll 1
-        for (int c4 = 2 * half; c4 < 2 * half + 2; ++c4) {
-          uint32_t s[32], d[32];
-          tmem_ld_x32(t_s + c4 * 32, s);
-          tmem_ld_x32(t_dp + c4 * 32, d);
-          tmem_wait_ld();
-          uint32_t ds[16];
+        const uint8_t* src = (half == 0 ? smem_res0 : smem_res1) + r * 128;
+        const uint32_t t_res = tmem_base + lane_field + (half == 0 ? C_RES0 : C_RES1);
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            float p0 = ex2_approx(fmaf(__uint_as_float(s[c]), p.qk_scale, -m_i));
-            float p1 = ex2_approx(fmaf(__uint_as_float(s[c + 1]), p.qk_scale, -m_i));
-            if (diag && c4 * 32 + c > r) p0 = 0.f;                 // key index > query index
-            if (diag && c4 * 32 + c + 1 > r) p1 = 0.f;
-            ds[c / 2] = pack_bf16x2(p0 * (__uint_as_float(d[c]) - d_i), p1 * (__uint_as_float(d[c + 1]) - d_i));
+        for (int bx = 0; bx < 2; ++bx) {
+          uint32_t w[32];
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint4 v4 = *reinterpret_cast<const uint4*>(src + bx * AT_BOX_BYTES + ((ch ^ (r & 7)) << 4));
+            w[4 * ch] = v4.x; w[4 * ch + 1] = v4.y; w[4 * ch + 2] = v4.z; w[4 * ch + 3] = v4.w;
           }
-          tmem_st_x16(t_s + bf16_col(c4 * 2), ds);   // packed inside this thread's own column half
+          tmem_st_x32(t_res + bx * 32, w);
         }
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_ready);
+        if (lane == 0) mbar_arrive(res_ready);
+      }
+      for (int sb = s_begin; ok && sb < s_end; ++sb, ++blocks) {
+        const bool diag = p.causal && sb == blk;
+        if (DKDV) {   // the step's M and delta vectors are read from shared memory below: observe their arrival directly
+          ok = mbar_wait(&st_full[stage], stage_phase, ctx, SITE + 8);
+          if (!ok) break;
+        }
+        ok = mbar_wait(&x_full[half], blocks & 1u, ctx, SITE + 6);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          const float* vec = DKDV ? reinterpret_cast<const float*>(smem_stage + stage * BW_STAGE_BYTES + 2 * BW_SUB_TILE) : nullptr;
+          const int col0 = half * BW_SUB;               // the step's first score, as an index into the streamed block
+          if (diag) score_step<DKDV, true>(t_buf, vec, p.qk_scale, m_i, d_i, col0, r);
+          else score_step<DKDV, false>(t_buf, vec, p.qk_scale, m_i, d_i, col0, r);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[half]);
+        stage += 2;                       // BW_NSTAGE is even: a group stays on stages of its own parity
+        if (stage >= BW_NSTAGE) { stage -= BW_NSTAGE; stage_phase ^= 1u; }
       }
       if (!ok) break;
-      // ---- epilogue: sm_scale * dQ -> bf16 -> staging in the Q tile -> TMA store
-      ok = mbar_wait(acc_full, items & 1u, ctx, 97);
+      // ---- epilogue: accumulators -> x scale -> bf16 -> staging in the resident tiles (no longer needed) -> TMA store
+      ok = mbar_wait(acc_full, items & 1u, ctx, SITE + 7);
       if (!ok) break;
       tc_fence_after();
-      store_acc(tmem_base + lane_field + C_DQ, p.sm_scale, smem_q, r, half);
+      store_acc(tmem_base + lane_field + C_ACC0, DKDV ? 1.0f : p.sm_scale, smem_res0, r, half);
+      if (DKDV) store_acc(tmem_base + lane_field + C_ACC1, p.sm_scale, smem_res1, r, half);
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(acc_empty);
-        const int y = hz * p.N_CTX + m * AT_BM + q * 32;
-        tma_store_2d(&tmap_dq, smem_q + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
+        const int y = hz * p.N_CTX + blk * AT_BM + q * 32;
+        tma_store_2d(&tmap_out0, smem_res0 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
+        if (DKDV) tma_store_2d(&tmap_out1, smem_res1 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
         tma_store_commit();
         tma_store_wait_read<0>();
         mbar_arrive(res_empty);
@@ -614,10 +536,16 @@ int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   const uint64_t rows = static_cast<uint64_t>(zh) * a.N_CTX;
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   int rc;
+  // resident tiles: boxes of 128 rows; streamed half-tiles: boxes of 64 rows; results: boxes of 32 rows (one warp's)
+  CUtensorMap tq_s, tk_s, tv_s, tdo_s;
   if ((rc = make_tmap_bf16_2d(&tq, a.q, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tk, a.k, BW_D, rows, BW_D, 64, AT_BN)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tv, a.v, BW_D, rows, BW_D, 64, AT_BN)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tk, a.k, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tv, a.v, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tdo, a.d_o, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tq_s, a.q, BW_D, rows, BW_D, 64, BW_SUB)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tk_s, a.k, BW_D, rows, BW_D, 64, BW_SUB)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tv_s, a.v, BW_D, rows, BW_D, 64, BW_SUB)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tdo_s, a.d_o, BW_D, rows, BW_D, 64, BW_SUB)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tdq, a.dq, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tdk, a.dk, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tdv, a.dv, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
@@ -643,15 +571,15 @@ int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   B200K_CHECK_LAUNCH("attn_bwd_delta_kernel");
 
   const int grid = p.num_items < dev->sm_count ? p.num_items : dev->sm_count;
-  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM_TOTAL));
-  attn_bwd_dkdv_tcgen05_kernel<<<grid, BW_THREADS, KV_SMEM_TOTAL, stream>>>(tq, tk, tv, tdo, tdk, tdv, p);
+  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BW_SMEM_TOTAL));
+  attn_bwd_tcgen05_kernel<true><<<grid, BW_THREADS, BW_SMEM_TOTAL, stream>>>(tk, tv, tq_s, tdo_s, tdv, tdk, p);
   count_launch();
-  B200K_CHECK_LAUNCH("attn_bwd_dkdv_tcgen05_kernel");
+  B200K_CHECK_LAUNCH("attn_bwd_tcgen05_kernel<dK, dV>");
 
-  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dq_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM_TOTAL));
-  attn_bwd_dq_tcgen05_kernel<<<grid, BW_THREADS, DQ_SMEM_TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
+  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BW_SMEM_TOTAL));
+  attn_bwd_tcgen05_kernel<false><<<grid, BW_THREADS, BW_SMEM_TOTAL, stream>>>(tq, tdo, tk_s, tv_s, tdq, tdq, p);
   count_launch();
-  B200K_CHECK_LAUNCH("attn_bwd_dq_tcgen05_kernel");
+  B200K_CHECK_LAUNCH("attn_bwd_tcgen05_kernel<dQ>");
   return B200K_OK;
 }
 
