@@ -275,7 +275,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-workload", default=None,
-                    choices=["matmul", "matmul_fused", "add", "sin", "attention", "attention_causal", "matmul_shard"],
+                    choices=["matmul", "matmul_fused", "add", "sin", "attention", "attention_causal", "matmul_shard",
+                             "attention_bwd"],
                     help="launch only this kernel warmup+steps times and print nothing to time: the small, "
                          "bounded command the ncu captures summarised under profiles/ are taken from")
     ap.add_argument("--shard-rows", type=int, default=1024, help="rows of A for --profile-workload matmul_shard")
@@ -460,6 +461,12 @@ def profile_workload(args, torch, ops, gi):
         n = 1 << 26
         x, y = torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
         fn = (lambda: ops.add(x, y)) if w == "add" else (lambda: ops.sin(x))
+    elif w == "attention_bwd":
+        # half the batch of the attention workload (2 x 32 heads x 4096 x 128): eight tensors of 67 MB, three launches
+        q = torch.randn(2, 32, 4096, 128, device="cuda").bfloat16()
+        k, v, d_o = torch.randn_like(q), torch.randn_like(q), torch.randn_like(q)
+        o, m = ops.attention_with_lse(q, k, v, False, 128 ** -0.5)
+        fn = lambda: ops.attention_backward(q, k, v, o, m, d_o, False, 128 ** -0.5)
     else:
         q = torch.randn(4, 32, 4096, 128, device="cuda").bfloat16()
         k, v = torch.randn_like(q), torch.randn_like(q)

@@ -706,7 +706,7 @@ def test_attention_backward_through_autograd_and_determinism():
 
 @pytest.mark.parametrize("causal", [False, True])
 def test_attention_backward_full_size_heads(causal):
-    # the full workload on the GPU; three (batch, head) pairs against fp32 autograd, canaries around the outputs
+    # the full workload on the GPU; three (batch, head) pairs against fp32 autograd
     Z, H, S, D = 4, 32, 4096, 128
     scale = D ** -0.5
     q, k, v = (t.cuda() for t in gi.attn_inputs(Z, H, S, D, seed=35))
@@ -720,6 +720,35 @@ def test_attention_backward_full_size_heads(causal):
         truth = _autograd_truth(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), d_o[sl].cpu(), causal, scale)
         for name, got, t in zip(("dq", "dk", "dv"), (dq, dk, dv), truth):
             assert float((got[sl].float() - t).norm() / t.norm()) <= 1e-2, (name, z, h)
+
+
+def test_attention_backward_cabi_writes_only_its_outputs():
+    # straight through the C-ABI with dq, dk, dv inside canary-filled buffers: every element written, nothing around them
+    Z, H, S, D = 2, 3, 256, 128
+    scale = D ** -0.5
+    q, k, v = (t.cuda() for t in gi.attn_inputs(Z, H, S, D, seed=36))
+    d_o = _d_o(Z, H, S, D).cuda()
+    o, m = ops.attention_with_lse(q, k, v, True, scale)
+    pad, n = 2048, q.numel()
+    bufs = [torch.full((n + 2 * pad,), -3.0, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    outs = [b[pad:pad + n].view(Z, H, S, D) for b in bufs]
+    for t in outs:
+        t.fill_(float("nan"))
+    delta = torch.empty(Z, H, S, device="cuda")
+    lib = _lib.load()
+    _lib.check(lib.b200k_attn_bwd_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), m.data_ptr(),
+                                       outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), delta.data_ptr(),
+                                       Z, H, S, D, 1, scale, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    want = ops.attention_backward(q, k, v, o, m, d_o, True, scale)
+    for b, got, w in zip(bufs, outs, want):
+        assert not torch.isnan(got.float()).any()
+        assert torch.equal(got.view(torch.int16), w.view(torch.int16))
+        assert bool((b[:pad] == -3.0).all()) and bool((b[pad + n:] == -3.0).all())
+    # delta = rowsum(o * dO) in fp32
+    ref_delta = (o.float() * d_o.float()).sum(-1)
+    assert float((delta - ref_delta).abs().max()) <= 1e-4 * float(ref_delta.abs().max()) + 1e-5
 
 
 def test_attention_backward_rejects_unsupported():
