@@ -13,20 +13,29 @@
 // Two kernels, both deterministic (no atomics): one CTA per 128-key block accumulates dK and dV over the query blocks,
 // one CTA per 128-query block accumulates dQ over the key blocks; each recomputes S and dP with tcgen05 MMAs.
 //
-//   warps 0-7  one thread per row of a step's score tile; warps 0-3 take the even steps, warps 4-7 the odd ones (the
-//              backward has no row reductions, M and delta are given): tcgen05.ld S and dP, exponentials, dS, bf16
-//              results written back over S / dP in tensor memory (packed over columns the thread has already read);
-//              epilogue (scale, downcast, swizzled staging, TMA store), one 64-column half per group
-//   warp 8     TMA producer (the item's resident tiles; a four-stage ring of the half-tiles that stream)
+//   warps 0-7  two threads per row of the 128 x 128 score tile (warps 0-3 columns 0-63, warps 4-7 columns 64-127; the
+//              backward has no row reductions, M and delta are given, so the halves never talk).  Phase 1: tcgen05.ld
+//              S, p = exp2(qk_scale S - M) kept in fp32 registers (dK/dV: bf16 P stored).  Phase 2: tcgen05.ld dP,
+//              dS = p (dP - delta) stored as bf16.  bf16 results go over the first 32 of the 64 columns the thread
+//              itself has read, so no warp writes where another still reads.  Epilogue: scale, downcast, swizzled
+//              staging, TMA store, one 64-column box per half
+//   warp 8     TMA producer
 //   warp 9     tensor-memory owner and tcgen05.mma issuer
-// Both kernels are one template.  The streamed dimension advances in steps of 64 rows (queries for dK/dV, keys for
-// dQ), so that a step's scores take 64 + 64 tensor-memory columns and two steps fit beside the accumulators:
-//   columns   0..127  step buffer 0: S | dP (64 fp32 columns each; bf16 P / dS packed over them)
-//   columns 128..255  step buffer 1
-//   columns 256..511  dK/dV kernel: dV | dK;  dQ kernel: dQ | Q, dO as bf16 MMA A operands (64 columns each)
-// The issuer runs one step ahead: MMA(S, dP) of step j+1 and the gradient MMAs of step j-1 execute while a score group
-// works on step j.  With whole 128-row blocks tensor memory held one block and the chain MMA -> exponentials -> MMA was
-// serial: 4.30 ms at Z=4, H=32, N_CTX=4096 against 3.30 ms now (dK/dV 1.95, dQ 1.29, delta 0.05).
+// All MMAs are 128 x 128 x 16: a 128 x 64 x 16 instruction occupies the tensor pipe for 46 cycles against 64 (measured),
+// so stepping the streamed dimension by 64 rows (which would let two whole score buffers fit in tensor memory) makes the
+// score products cost 1.4 times as much; that version ran at 3.30 ms (Z=4, H=32, N_CTX=4096), the serial whole-block
+// version before it at 4.30 ms.  Instead the 512 columns are used so that the pipe always has work that does not depend
+// on the phase the score warps are in:
+//   dK/dV  S^T | dP^T | dV | dK.  Phase 1 leaves p in registers, so the issuer can run the NEXT block's S^T while phase 2
+//          works; phase 2 writes dS^T and P^T over the dP^T columns it has read, then the issuer runs dV += P^T dO,
+//          dK += dS^T Q and the next dP^T (while the next phase 1 runs).
+//   dQ     S (buffer 0) | S (buffer 1) | dP | dQ.  The next block's S is always ready; after phase 2 (dS over S) the
+//          issuer runs the next dP, dQ += dS K and the S after next.
+// Measured (Z=4, H=32, N_CTX=4096): 2.9 ms = 940 TFLOP/s of the algorithm's flop; cycle stamps show the dQ kernel bound
+// by its score warps (phase 1 1240 + phase 2 430 cycles per block, hand-offs 300-450) and the dK/dV kernel by the chain
+// phase 2 -> 16 gradient MMAs + 8 for dP^T -> phase 2.  A microbenchmark of the issue loop puts the MMAs themselves at
+// 64-67 cycles whatever the other warps do (exponentials, tcgen05.ld / st, TMA fills); each dependent group of 8 costs
+// about 420 cycles more between the barrier that releases it and the barrier it completes.
 #include <math.h>
 #include <string.h>
 
@@ -40,18 +49,7 @@ constexpr int BW_D = 128;
 constexpr int BW_THREADS = 320;
 constexpr int BW_SCORE_WARPS = 8;
 constexpr int BW_WARP_TMA = 8, BW_WARP_MMA = 9;
-constexpr int BW_TILE_BYTES = AT_BM * BW_D * 2;       // 32 KB: two boxes of 128 rows x 64 columns (resident tiles)
-constexpr int BW_SUB = 64;                            // streamed rows per step
-constexpr int BW_SUB_BOX = BW_SUB * 128;              // 8 KB: 64 rows x 64 columns
-constexpr int BW_SUB_TILE = 2 * BW_SUB_BOX;           // 16 KB: 64 rows x 128 columns
-constexpr int BW_NSTAGE = 4;
-static_assert(BW_NSTAGE % 2 == 0, "the two score groups own alternate stages");
-constexpr int BW_STAGE_BYTES = 2 * BW_SUB_TILE + 1024;   // two half-tiles, then 64 M values and 64 delta values (dK/dV)
-constexpr int BW_STAGE_OFF = 2 * BW_TILE_BYTES;          // after the two resident tiles
-constexpr int BW_BAR_OFF = BW_STAGE_OFF + BW_NSTAGE * BW_STAGE_BYTES;
-constexpr int BW_NBAR = 2 + 2 * BW_NSTAGE + 2 + 2 + 2 + 1;
-constexpr int BW_SMEM_TOTAL = BW_BAR_OFF + BW_NBAR * 8 + 16 + 1024;
-static_assert(BW_SMEM_TOTAL <= 232448, "attention backward shared memory budget exceeded");
+constexpr int BW_TILE_BYTES = AT_BM * BW_D * 2;       // 32 KB: two boxes of 128 rows x 64 columns
 
 struct BwdParams {
   int ZH, N_CTX, num_blk;
@@ -91,24 +89,22 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
                : "memory");
 }
 
-// Descriptor offsets (16-byte units) of the k-step `kk` (16 elements of the contraction) inside a tile of two
-// 64-column boxes of `box_bytes` each: contraction along the tile's columns (K-major operand) / along its rows
-// (MN-major operand).
-__device__ __forceinline__ uint64_t koff_cols(int kk, int box_bytes) {
-  return static_cast<uint64_t>(((kk >> 2) * box_bytes + (kk & 3) * 32) >> 4);
+// Descriptor offsets (16-byte units) of the k-step `kk` (16 elements of the contraction) inside a 128 x 128 tile of two
+// 64-column boxes: contraction along the tile's columns (K-major operand) / along its rows (MN-major operand).
+__device__ __forceinline__ uint64_t koff_cols(int kk) {
+  return static_cast<uint64_t>(((kk >> 2) * AT_BOX_BYTES + (kk & 3) * 32) >> 4);
 }
 __device__ __forceinline__ uint64_t koff_rows(int kk) { return static_cast<uint64_t>((kk * 2048) >> 4); }
 
-// A tile of `rows` x 128 columns: two TMA boxes of 64 columns.
-__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row, int box_bytes) {
+// One 128 x 128 tile: two TMA boxes.
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row) {
   tma_load_2d(dst, m, bar, 0, row);
-  tma_load_2d(dst + box_bytes, m, bar, 64, row);
+  tma_load_2d(dst + AT_BOX_BYTES, m, bar, 64, row);
 }
 
-// Tensor-memory column (relative to a step's fp32 score tile of 64 columns) of the bf16 operand's k-step kk (16 scores
-// = 8 columns): each thread packs its 32 scores at the start of its own 32 columns, so no warp writes where another
-// still reads.
-__device__ __forceinline__ constexpr uint32_t bf16_col(int kk) { return (kk >> 1) * 32 + (kk & 1) * 8; }
+// Tensor-memory column (relative to a 128-column fp32 tile) of the bf16 operand's k-step kk (16 values = 8 columns):
+// each column half is packed over the first 32 of its own 64 columns.
+__device__ __forceinline__ constexpr uint32_t bf16_col(int kk) { return kk < 4 ? kk * 8 : 64 + (kk - 4) * 8; }
 
 // Epilogue of one accumulator: 128 rows x 128 fp32 columns of tensor memory -> x scale -> bf16 -> swizzled staging in
 // shared memory (a resident tile that is no longer needed); each thread takes the 64-column box `half` of its row and
@@ -133,118 +129,160 @@ __device__ __forceinline__ void store_acc(uint32_t t_acc, float scale, uint8_t* 
   }
 }
 
-// The score work of one thread for one step: its row's 64 fp32 scores S and 64 values dP in the step buffer `t_buf`
-// (S at columns 0..63, dP at 64..127) become bf16 dS (and P for dK/dV), packed over the first 16 columns of every 32
-// just read.  Sixteen columns at a time, the next sixteen in flight meanwhile; pairs of scores go through the packed
-// fp32 instructions (each lane rounds like the scalar form), because the issue slots beside the exponentials are
-// what bounds this loop (about 9 cycles per exponential with two other instructions, 14 with four).
-//   dK/dV (rows = keys): M and delta differ per column and come from shared memory: p = exp2(-(M - s * qk_scale)),
-//                        dS = p * (dP - delta); masked (diagonal block) where query < key
-//   dQ (rows = queries): M and delta are this thread's: p = exp2(s * qk_scale - M); masked where key > query
-template <bool DKDV, bool MASKED>
-__device__ __forceinline__ void score_step(uint32_t t_buf, const float* vec, float qk_scale, float m_i, float d_i, int col0,
-                                           int r) {
-  const uint64_t scale2 = DKDV ? pack_f32x2(-qk_scale, -qk_scale) : pack_f32x2(qk_scale, qk_scale);
-  const uint64_t negm2 = pack_f32x2(-m_i, -m_i), negd2 = pack_f32x2(-d_i, -d_i);
-  const uint64_t minus1 = pack_f32x2(-1.0f, -1.0f);
-  uint32_t s[2][16], d[2][16];
-  uint32_t pp[16], ds[16];
-  tmem_ld_x16(t_buf, s[0]);
-  tmem_ld_x16(t_buf + 64, d[0]);
+// Phase 1 of a thread's 64 scores at tensor-memory address t_s: p = exp2(qk_scale * s - M), fp32, into pr[].  Sixteen
+// columns at a time with the next sixteen in flight; pairs go through the packed fp32 instructions (each lane rounds
+// like the scalar form) because the issue slots beside the exponentials are what bounds this loop.
+//   COLS (dK/dV: rows = keys): M differs per column, read from shared memory (mvec); masked where query < key
+//   !COLS (dQ: rows = queries): M is this thread's (m_i); masked where key > query
+// col0 is the index of the thread's first column inside the block, r the thread's row.
+template <bool COLS, bool MASKED>
+__device__ __forceinline__ void score_phase1(uint32_t t_s, const float* mvec, float qk_scale, float m_i, int col0, int r,
+                                             float (&pr)[64]) {
+  const uint64_t scale2 = COLS ? pack_f32x2(-qk_scale, -qk_scale) : pack_f32x2(qk_scale, qk_scale);
+  const uint64_t negm2 = pack_f32x2(-m_i, -m_i);
+  uint32_t in[2][16];
+  tmem_ld_x16(t_s, in[0]);
   tmem_wait_ld();
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    if (k + 1 < 4) {
-      tmem_ld_x16(t_buf + (k + 1) * 16, s[(k + 1) & 1]);
-      tmem_ld_x16(t_buf + 64 + (k + 1) * 16, d[(k + 1) & 1]);
-    }
-    const uint32_t(&sk)[16] = s[k & 1];
-    const uint32_t(&dk)[16] = d[k & 1];
+    if (k + 1 < 4) tmem_ld_x16(t_s + (k + 1) * 16, in[(k + 1) & 1]);
+    const uint32_t(&sk)[16] = in[k & 1];
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
       const uint64_t s2 = pack_f32x2(__uint_as_float(sk[c]), __uint_as_float(sk[c + 1]));
-      const uint64_t d2 = pack_f32x2(__uint_as_float(dk[c]), __uint_as_float(dk[c + 1]));
       float x0, x1, p0, p1;
-      uint64_t t2;
-      if (DKDV) {
-        const float2 m2 = *reinterpret_cast<const float2*>(vec + k * 16 + c);
-        const float2 dl2 = *reinterpret_cast<const float2*>(vec + 64 + k * 16 + c);
+      if (COLS) {
+        const float2 m2 = *reinterpret_cast<const float2*>(mvec + k * 16 + c);
         unpack_f32x2(fma_f32x2(s2, scale2, pack_f32x2(m2.x, m2.y)), x0, x1);     // M - s * qk_scale
         p0 = ex2_approx(-x0);
         p1 = ex2_approx(-x1);
-        t2 = fma_f32x2(pack_f32x2(dl2.x, dl2.y), minus1, d2);                     // dP - delta
         if (MASKED) {
-          if (col0 + k * 16 + c < r) p0 = 0.f;                                    // query index < key index
+          if (col0 + k * 16 + c < r) p0 = 0.f;
           if (col0 + k * 16 + c + 1 < r) p1 = 0.f;
         }
-        pp[(k & 1) * 8 + c / 2] = pack_bf16x2(p0, p1);
       } else {
         unpack_f32x2(fma_f32x2(s2, scale2, negm2), x0, x1);
         p0 = ex2_approx(x0);
         p1 = ex2_approx(x1);
-        t2 = add_f32x2(d2, negd2);
         if (MASKED) {
-          if (col0 + k * 16 + c > r) p0 = 0.f;                                    // key index > query index
+          if (col0 + k * 16 + c > r) p0 = 0.f;
           if (col0 + k * 16 + c + 1 > r) p1 = 0.f;
         }
       }
-      float y0, y1;
-      unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), t2), y0, y1);
-      ds[(k & 1) * 8 + c / 2] = pack_bf16x2(y0, y1);
-    }
-    if (k & 1) {   // 32 scores done: 16 columns of bf16 over the start of the 32 columns they came from
-      if (DKDV) {
-        tmem_st_x16(t_buf + (k >> 1) * 32, pp);
-        tmem_st_x16(t_buf + 64 + (k >> 1) * 32, ds);
-      } else {
-        tmem_st_x16(t_buf + (k >> 1) * 32, ds);
-      }
+      pr[k * 16 + c] = p0;
+      pr[k * 16 + c + 1] = p1;
     }
     if (k + 1 < 4) tmem_wait_ld();
   }
 }
 
+// 64 fp32 values -> 32 columns of bf16 pairs at t_dst.
+__device__ __forceinline__ void store_bf16_64(uint32_t t_dst, const float (&v)[64]) {
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    uint32_t w[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c) w[c] = pack_bf16x2(v[g * 32 + 2 * c], v[g * 32 + 2 * c + 1]);
+    tmem_st_x16(t_dst + g * 16, w);
+  }
+}
+
+// Phase 2: dS = p * (dP - delta) for the thread's 64 values of dP at t_dp; bf16 result to the 32 columns at t_dst.
+template <bool COLS>
+__device__ __forceinline__ void score_phase2(uint32_t t_dp, uint32_t t_dst, const float* dvec, float d_i, const float (&pr)[64]) {
+  const uint64_t negd2 = pack_f32x2(-d_i, -d_i);
+  const uint64_t minus1 = pack_f32x2(-1.0f, -1.0f);
+  uint32_t in[2][16];
+  uint32_t ds[16];
+  tmem_ld_x16(t_dp, in[0]);
+  tmem_wait_ld();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (k + 1 < 4) tmem_ld_x16(t_dp + (k + 1) * 16, in[(k + 1) & 1]);
+    const uint32_t(&dk)[16] = in[k & 1];
+#pragma unroll
+    for (int c = 0; c < 16; c += 2) {
+      const uint64_t d2 = pack_f32x2(__uint_as_float(dk[c]), __uint_as_float(dk[c + 1]));
+      uint64_t t2;
+      if (COLS) {
+        const float2 dl2 = *reinterpret_cast<const float2*>(dvec + k * 16 + c);
+        t2 = fma_f32x2(pack_f32x2(dl2.x, dl2.y), minus1, d2);                     // dP - delta
+      } else {
+        t2 = add_f32x2(d2, negd2);
+      }
+      float y0, y1;
+      unpack_f32x2(mul_f32x2(pack_f32x2(pr[k * 16 + c], pr[k * 16 + c + 1]), t2), y0, y1);
+      ds[(k & 1) * 8 + c / 2] = pack_bf16x2(y0, y1);
+    }
+    if (k & 1) tmem_st_x16(t_dst + (k >> 1) * 16, ds);
+    if (k + 1 < 4) tmem_wait_ld();
+  }
+}
+
+// Common epilogue of a score warp: one or two accumulators -> staging in the resident tiles -> TMA stores of the
+// warp's 32 rows x 64 columns; then the resident tiles and the accumulators are handed back.
+__device__ __forceinline__ void epilogue_store(uint32_t t_acc0, float scale0, uint8_t* stage0, const CUtensorMap* out0,
+                                               bool two, uint32_t t_acc1, float scale1, uint8_t* stage1,
+                                               const CUtensorMap* out1, int r, int q, int half, int y, uint32_t lane,
+                                               uint64_t* acc_empty, uint64_t* res_empty) {
+  store_acc(t_acc0, scale0, stage0, r, half);
+  if (two) store_acc(t_acc1, scale1, stage1, r, half);
+  tc_fence_before();
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    mbar_arrive(acc_empty);
+    tma_store_2d(out0, stage0 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
+    if (two) tma_store_2d(out1, stage1 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
+    tma_store_commit();
+    tma_store_wait_read<0>();
+    mbar_arrive(res_empty);
+  }
+  __syncwarp();
+}
+
 // ---------------------------------------------------------------------------------------------------------------
-// DKDV = true:  one item = (batch*head, key block n); resident K, V; the queries stream (blocks m >= n when causal):
-//               S^T = K Qs^T, dP^T = V dOs^T (rows = keys), dV += P^T dOs, dK += dS^T Qs.
-// DKDV = false: one item = (batch*head, query block m); resident Q, dO; the keys stream (blocks n <= m when causal):
-//               S = Q Ks^T, dP = dO Vs^T (rows = queries), dQ += dS Ks.
-// "res0/res1" are the resident pair, "str0/str1" the streamed pair (the factor of res0 / res1 in the score products),
-// "out0/out1" the results (dV, dK or dQ, -).
+// dK and dV: one item = (batch*head, key block n); K, V resident; the query blocks m stream (m >= n when causal).
+// Rows of the score tiles are keys: S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q.
 // ---------------------------------------------------------------------------------------------------------------
-template <bool DKDV>
+constexpr int KV_NSTAGE = 2;
+constexpr int KV_Q_OFF = 2 * BW_TILE_BYTES;                           // after the resident K and V tiles
+constexpr int KV_DO_OFF = KV_Q_OFF + KV_NSTAGE * BW_TILE_BYTES;
+constexpr int KV_VEC_OFF = KV_DO_OFF + KV_NSTAGE * BW_TILE_BYTES;     // per stage 128 M values, 128 delta values
+constexpr int KV_BAR_OFF = KV_VEC_OFF + KV_NSTAGE * 1024;
+constexpr int KV_NBAR = 2 + 4 * KV_NSTAGE + 6;
+constexpr int KV_SMEM_TOTAL = KV_BAR_OFF + KV_NBAR * 8 + 16 + 1024;
+static_assert(KV_SMEM_TOTAL <= 232448, "attention backward (dK/dV) shared memory budget exceeded");
+
 __global__ void __launch_bounds__(BW_THREADS, 1)
-attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_res0, const __grid_constant__ CUtensorMap tmap_res1,
-                        const __grid_constant__ CUtensorMap tmap_str0, const __grid_constant__ CUtensorMap tmap_str1,
-                        const __grid_constant__ CUtensorMap tmap_out0, const __grid_constant__ CUtensorMap tmap_out1,
-                        const BwdParams p) {
-  constexpr uint32_t IDESC_X = umma_idesc_bf16_f32(AT_BM, BW_SUB, 0, 0);   // scores: both operands K-major, N = 64
-  constexpr uint32_t IDESC_G = umma_idesc_bf16_f32(AT_BM, BW_D, 0, 1);     // gradients: A in tensor memory, B MN-major
-  constexpr uint32_t C_ACC0 = 256, C_ACC1 = 384;
-  // dQ has one accumulator, so its resident tiles (Q, dO) fit in tensor memory as bf16 A operands (64 columns each):
-  // the score MMAs then read only the streamed half-tile from shared memory (32 KB per step instead of 96 KB; shared
-  // memory bandwidth, 128 bytes per clock, is what bounds these MMAs at N = 64).  dK/dV has no columns to spare.
-  constexpr bool RES_TMEM = !DKDV;
-  constexpr uint32_t C_RES0 = 384, C_RES1 = 448;
-  constexpr uint32_t STAGE_TX = 2 * BW_SUB_TILE + (DKDV ? 512 : 0);
-  // wait sites: 80.. for dK/dV, 90.. for dQ
-  constexpr uint32_t SITE = DKDV ? 80 : 90;
+attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                             const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                             const __grid_constant__ CUtensorMap tmap_dk, const __grid_constant__ CUtensorMap tmap_dv,
+                             const BwdParams p) {
+  constexpr uint32_t IDESC_SS = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);   // both operands K-major
+  constexpr uint32_t IDESC_TS = umma_idesc_bf16_f32(AT_BM, BW_D, 0, 1);    // A in tensor memory, B MN-major
+  constexpr uint32_t C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 384;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_res0 = smem;
-  uint8_t* smem_res1 = smem + BW_TILE_BYTES;
-  uint8_t* smem_stage = smem + BW_STAGE_OFF;
-  uint64_t* res_full = reinterpret_cast<uint64_t*>(smem + BW_BAR_OFF);   // resident tiles have arrived
+  uint8_t* smem_k = smem;
+  uint8_t* smem_v = smem + BW_TILE_BYTES;
+  uint8_t* smem_q = smem + KV_Q_OFF;
+  uint8_t* smem_do = smem + KV_DO_OFF;
+  float* smem_vec = reinterpret_cast<float*>(smem + KV_VEC_OFF);
+  uint64_t* res_full = reinterpret_cast<uint64_t*>(smem + KV_BAR_OFF);   // K and V tiles have arrived
   uint64_t* res_empty = res_full + 1;                                    // ... may be overwritten (8 warps)
-  uint64_t* st_full = res_empty + 1;                                     // [stage] the step's half-tiles have arrived
-  uint64_t* st_empty = st_full + BW_NSTAGE;                              // [stage] released by the MMA issuer
-  uint64_t* x_full = st_empty + BW_NSTAGE;                               // [buffer] S and dP are in tensor memory
-  uint64_t* p_ready = x_full + 2;                                        // [buffer] bf16 P / dS written (4 warps)
-  uint64_t* acc_full = p_ready + 2;                                      // accumulators complete
+  uint64_t* q_full = res_empty + 1;                                      // [stage] Q tile, M and delta vectors
+  uint64_t* q_empty = q_full + KV_NSTAGE;                                // [stage] released after dK += dS^T Q
+  uint64_t* do_full = q_empty + KV_NSTAGE;                               // [stage] dO tile
+  uint64_t* do_empty = do_full + KV_NSTAGE;                              // [stage] released after dV += P^T dO
+  uint64_t* s_full = do_empty + KV_NSTAGE;                               // S^T is in tensor memory
+  uint64_t* dp_full = s_full + 1;                                        // dP^T is in tensor memory
+  uint64_t* p1_ready = dp_full + 1;                                      // S^T consumed (8 warps)
+  uint64_t* p2_ready = p1_ready + 1;                                     // dS^T and P^T written over dP^T (8 warps)
+  uint64_t* acc_full = p2_ready + 1;                                     // dV and dK complete
   uint64_t* acc_empty = acc_full + 1;                                    // ... read out (8 warps)
-  uint64_t* res_ready = acc_empty + 1;                                   // resident tiles copied to tensor memory (8 warps)
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(res_ready + 1);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_empty + 1);
   uint32_t* abort_smem = tmem_ptr_smem + 1;
 
   const int warp_idx = threadIdx.x >> 5;
@@ -254,23 +292,24 @@ attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_res0, const __g
   if (threadIdx.x == 0) {
     mbar_init(res_full, 1);
     mbar_init(res_empty, BW_SCORE_WARPS);
-    for (int s = 0; s < BW_NSTAGE; ++s) {
-      mbar_init(&st_full[s], 1);
-      mbar_init(&st_empty[s], 1);
+    for (int s = 0; s < KV_NSTAGE; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+      mbar_init(&do_full[s], 1);
+      mbar_init(&do_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&x_full[b], 1);
-      mbar_init(&p_ready[b], BW_SCORE_WARPS / 2);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p1_ready, BW_SCORE_WARPS);
+    mbar_init(p2_ready, BW_SCORE_WARPS);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, BW_SCORE_WARPS);
-    mbar_init(res_ready, BW_SCORE_WARPS);
     *abort_smem = 0;
     fence_mbar_init();
-    prefetch_tmap(&tmap_res0);
-    prefetch_tmap(&tmap_res1);
-    prefetch_tmap(&tmap_str0);
-    prefetch_tmap(&tmap_str1);
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_do);
   }
   if (warp_idx == BW_WARP_MMA) {
     tmem_alloc(tmem_ptr_smem, 512);
@@ -281,222 +320,420 @@ attn_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_res0, const __g
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  // item -> (batch*head, resident block, range of streamed blocks).  Causal items differ in length: the long ones
-  // are handed out first (dK/dV: small n; dQ: large m).
-  auto item_range = [&](int item, int& hz, int& blk, int& s_begin, int& s_end) {
-    hz = item / p.num_blk;
-    blk = item - hz * p.num_blk;
-    if (DKDV) {
-      s_begin = p.causal ? blk : 0;
-      s_end = p.num_blk;
-    } else {
-      if (p.causal) blk = p.num_blk - 1 - blk;
-      s_begin = 0;
-      s_end = p.causal ? blk + 1 : p.num_blk;
-    }
-  };
-
+  // Every role walks the same sequence of (item, block) and counts blocks in `g`: stage g % 2 (use g / 2 of it), and
+  // the g-th completion of the single barriers.
   if (warp_idx == BW_WARP_TMA) {
     // ------------------------------------------------------------------ TMA producer
-    int stage = 0;
-    uint32_t stage_phase = 0, items = 0;
+    uint32_t items = 0, g = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      int hz, blk, s_begin, s_end;
-      item_range(item, hz, blk, s_begin, s_end);
+      const int hz = item / p.num_blk, n = item - hz * p.num_blk;
       const int row_base = hz * p.N_CTX;
-      ok = mbar_wait(res_empty, (items & 1u) ^ 1u, ctx, SITE + 0);
+      ok = mbar_wait(res_empty, (items & 1u) ^ 1u, ctx, 80);
       if (!ok) break;
       if (lane == 0) {
         mbar_expect_tx(res_full, 2 * BW_TILE_BYTES);
-        load_tile(smem_res0, &tmap_res0, res_full, row_base + blk * AT_BM, AT_BOX_BYTES);
-        load_tile(smem_res1, &tmap_res1, res_full, row_base + blk * AT_BM, AT_BOX_BYTES);
+        load_tile(smem_k, &tmap_k, res_full, row_base + n * AT_BN);
+        load_tile(smem_v, &tmap_v, res_full, row_base + n * AT_BN);
       }
       __syncwarp();
-      for (int step = 2 * s_begin; ok && step < 2 * s_end; ++step) {
-        ok = mbar_wait(&st_empty[stage], stage_phase ^ 1u, ctx, SITE + 1);
+      for (int m = p.causal ? n : 0; ok && m < p.num_blk; ++m, ++g) {
+        const uint32_t st = g & 1u, ph = (g >> 1) & 1u;
+        const int row = row_base + m * AT_BM;
+        ok = mbar_wait(&q_empty[st], ph ^ 1u, ctx, 81);
         if (!ok) break;
         if (lane == 0) {
-          uint8_t* dst = smem_stage + stage * BW_STAGE_BYTES;
-          const int row = row_base + step * BW_SUB;
-          mbar_expect_tx(&st_full[stage], STAGE_TX);
-          load_tile(dst, &tmap_str0, &st_full[stage], row, BW_SUB_BOX);
-          load_tile(dst + BW_SUB_TILE, &tmap_str1, &st_full[stage], row, BW_SUB_BOX);
-          if (DKDV) {
-            bulk_load_1d(dst + 2 * BW_SUB_TILE, p.lse2 + row, 256, &st_full[stage]);
-            bulk_load_1d(dst + 2 * BW_SUB_TILE + 256, p.delta + row, 256, &st_full[stage]);
-          }
+          mbar_expect_tx(&q_full[st], BW_TILE_BYTES + 1024);
+          load_tile(smem_q + st * BW_TILE_BYTES, &tmap_q, &q_full[st], row);
+          bulk_load_1d(smem_vec + st * 256, p.lse2 + row, 512, &q_full[st]);
+          bulk_load_1d(smem_vec + st * 256 + 128, p.delta + row, 512, &q_full[st]);
         }
         __syncwarp();
-        if (++stage == BW_NSTAGE) { stage = 0; stage_phase ^= 1u; }
+        ok = mbar_wait(&do_empty[st], ph ^ 1u, ctx, 82);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(&do_full[st], BW_TILE_BYTES);
+          load_tile(smem_do + st * BW_TILE_BYTES, &tmap_do, &do_full[st], row);
+        }
+        __syncwarp();
       }
     }
   } else if (warp_idx == BW_WARP_MMA) {
     // ------------------------------------------------------------------ MMA issuer
-    int xs = 0, gs = 0;                 // ring positions of the next score step / the next gradient step
-    uint32_t xs_phase = 0, items = 0, blocks = 0;
+    uint32_t items = 0, g = 0;
     bool ok = true;
-    const uint64_t r0_desc = umma_smem_desc_sw128(smem_u32(smem_res0), 16, 1024);
-    const uint64_t r1_desc = umma_smem_desc_sw128(smem_u32(smem_res1), 16, 1024);
+    const uint64_t k_desc = umma_smem_desc_sw128(smem_u32(smem_k), 16, 1024);
+    const uint64_t v_desc = umma_smem_desc_sw128(smem_u32(smem_v), 16, 1024);
+    // S^T = K Q^T / dP^T = V dO^T of the block in stage st: rows = keys, columns = queries, contraction over d
+    auto issue_st = [&](uint32_t st) {
+      const uint64_t qk = umma_smem_desc_sw128(smem_u32(smem_q + st * BW_TILE_BYTES), 16, 1024);
+#pragma unroll
+      for (int kk = 0; kk < BW_D / 16; ++kk)
+        umma_ss(tmem_base + C_ST, k_desc + koff_cols(kk), qk + koff_cols(kk), IDESC_SS, kk > 0 ? 1u : 0u);
+      umma_commit(s_full);
+    };
+    auto issue_dpt = [&](uint32_t st) {
+      const uint64_t dok = umma_smem_desc_sw128(smem_u32(smem_do + st * BW_TILE_BYTES), 16, 1024);
+#pragma unroll
+      for (int kk = 0; kk < BW_D / 16; ++kk)
+        umma_ss(tmem_base + C_DPT, v_desc + koff_cols(kk), dok + koff_cols(kk), IDESC_SS, kk > 0 ? 1u : 0u);
+      umma_commit(dp_full);
+    };
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      int hz, blk, s_begin, s_end;
-      item_range(item, hz, blk, s_begin, s_end);
-      ok = mbar_wait(RES_TMEM ? res_ready : res_full, items & 1u, ctx, SITE + 2);
+      const int hz = item / p.num_blk, n = item - hz * p.num_blk;
+      (void)hz;
+      const int nb = p.num_blk - (p.causal ? n : 0);
+      ok = mbar_wait(res_full, items & 1u, ctx, 83);
+      if (!ok) break;
+      // the item's first block: both score products up front
+      ok = mbar_wait(&q_full[g & 1u], (g >> 1) & 1u, ctx, 84);
       if (!ok) break;
       tc_fence_after();
-      const int total = 2 * (s_end - s_begin);
-      for (int j = 0; ok && j <= total; ++j) {
-        if (j < total) {
-          // scores of step j into buffer j & 1.  Its previous user (step j - 2) has been read by the score warps
-          // (p_ready was observed) and its gradient MMAs were issued before these; the tensor pipe runs in order
-          ok = mbar_wait(&st_full[xs], xs_phase, ctx, SITE + 3);
+      if (lane == 0) issue_st(g & 1u);
+      __syncwarp();
+      ok = mbar_wait(&do_full[g & 1u], (g >> 1) & 1u, ctx, 85);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) issue_dpt(g & 1u);
+      __syncwarp();
+      for (int j = 0; ok && j < nb; ++j, ++g) {
+        const uint32_t st = g & 1u, nst = (g + 1) & 1u, nph = ((g + 1) >> 1) & 1u;
+        const bool more = j + 1 < nb;
+        // ---- after phase 1 (S^T is in the score warps' registers): the next block's S^T
+        ok = mbar_wait(p1_ready, g & 1u, ctx, 86);
+        if (!ok) break;
+        if (more) {
+          ok = mbar_wait(&q_full[nst], nph, ctx, 84);
           if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
-            const uint32_t a0 = smem_u32(smem_stage + xs * BW_STAGE_BYTES);
-            const uint64_t s0 = umma_smem_desc_sw128(a0, 16, 1024), s1 = umma_smem_desc_sw128(a0 + BW_SUB_TILE, 16, 1024);
-            const uint32_t t = tmem_base + (j & 1) * 128;
-            if (RES_TMEM) {
-#pragma unroll
-              for (int kk = 0; kk < BW_D / 16; ++kk)
-                umma_ts(t, tmem_base + C_RES0 + kk * 8, s0 + koff_cols(kk, BW_SUB_BOX), IDESC_X, kk > 0 ? 1u : 0u);
-#pragma unroll
-              for (int kk = 0; kk < BW_D / 16; ++kk)
-                umma_ts(t + 64, tmem_base + C_RES1 + kk * 8, s1 + koff_cols(kk, BW_SUB_BOX), IDESC_X, kk > 0 ? 1u : 0u);
-            } else {
-#pragma unroll
-              for (int kk = 0; kk < BW_D / 16; ++kk)
-                umma_ss(t, r0_desc + koff_cols(kk, AT_BOX_BYTES), s0 + koff_cols(kk, BW_SUB_BOX), IDESC_X, kk > 0 ? 1u : 0u);
-#pragma unroll
-              for (int kk = 0; kk < BW_D / 16; ++kk)
-                umma_ss(t + 64, r1_desc + koff_cols(kk, AT_BOX_BYTES), s1 + koff_cols(kk, BW_SUB_BOX), IDESC_X, kk > 0 ? 1u : 0u);
-            }
-            umma_commit(&x_full[j & 1]);
-          }
+          if (lane == 0) issue_st(nst);
           __syncwarp();
-          if (++xs == BW_NSTAGE) { xs = 0; xs_phase ^= 1u; }
         }
-        if (j > 0) {
-          // gradients of step j - 1: A = bf16 P / dS in tensor memory (8 columns per k-step of 16 streamed rows)
-          const int jj = j - 1;
-          ok = mbar_wait(&p_ready[jj & 1], (blocks + (jj >> 1)) & 1u, ctx, SITE + 4);
+        // ---- after phase 2 (dS^T | P^T in the dP^T columns): dV += P^T dO, dK += dS^T Q, then the next block's dP^T
+        ok = mbar_wait(p2_ready, g & 1u, ctx, 88);
+        if (!ok) break;
+        if (j == 0) {   // the previous item's dV / dK must have left tensor memory before they are overwritten
+          ok = mbar_wait(acc_empty, (items & 1u) ^ 1u, ctx, 87);
           if (!ok) break;
-          if (jj == 0) {   // the previous item's accumulators must have left tensor memory before they are overwritten
-            ok = mbar_wait(acc_empty, (items & 1u) ^ 1u, ctx, SITE + 5);
-            if (!ok) break;
-          }
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint64_t don = umma_smem_desc_sw128(smem_u32(smem_do + st * BW_TILE_BYTES), AT_BOX_BYTES, 1024);
+          const uint64_t qn = umma_smem_desc_sw128(smem_u32(smem_q + st * BW_TILE_BYTES), AT_BOX_BYTES, 1024);
+#pragma unroll
+          for (int kk = 0; kk < AT_BM / 16; ++kk)
+            umma_ts(tmem_base + C_DV, tmem_base + C_DPT + 32 + bf16_col(kk), don + koff_rows(kk), IDESC_TS, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&do_empty[st]);
+#pragma unroll
+          for (int kk = 0; kk < AT_BM / 16; ++kk)
+            umma_ts(tmem_base + C_DK, tmem_base + C_DPT + bf16_col(kk), qn + koff_rows(kk), IDESC_TS, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&q_empty[st]);
+          if (!more) umma_commit(acc_full);
+        }
+        __syncwarp();
+        if (more) {
+          ok = mbar_wait(&do_full[nst], nph, ctx, 85);
+          if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
-            const uint32_t a0 = smem_u32(smem_stage + gs * BW_STAGE_BYTES);
-            const uint64_t n0 = umma_smem_desc_sw128(a0, BW_SUB_BOX, 1024);
-            const uint64_t n1 = umma_smem_desc_sw128(a0 + BW_SUB_TILE, BW_SUB_BOX, 1024);
-            const uint32_t t = tmem_base + (jj & 1) * 128;
-            if (DKDV) {
-#pragma unroll
-              for (int kk = 0; kk < BW_SUB / 16; ++kk)   // dV += P^T dOs
-                umma_ts(tmem_base + C_ACC0, t + bf16_col(kk), n1 + koff_rows(kk), IDESC_G, (jj > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-              for (int kk = 0; kk < BW_SUB / 16; ++kk)   // dK += dS^T Qs
-                umma_ts(tmem_base + C_ACC1, t + 64 + bf16_col(kk), n0 + koff_rows(kk), IDESC_G, (jj > 0 || kk > 0) ? 1u : 0u);
-            } else {
-#pragma unroll
-              for (int kk = 0; kk < BW_SUB / 16; ++kk)   // dQ += dS Ks
-                umma_ts(tmem_base + C_ACC0, t + bf16_col(kk), n0 + koff_rows(kk), IDESC_G, (jj > 0 || kk > 0) ? 1u : 0u);
-            }
-            umma_commit(&st_empty[gs]);
-            if (jj == total - 1) umma_commit(acc_full);
-          }
+          if (lane == 0) issue_dpt(nst);
           __syncwarp();
-          if (++gs == BW_NSTAGE) gs = 0;
         }
       }
-      blocks += static_cast<uint32_t>(s_end - s_begin);
     }
   } else {
-    // ------------------------------------------------------------------ score rows (warps 0..7)
-    // warps 0-3 take the even steps (buffer 0), warps 4-7 the odd ones (buffer 1): the two warps that share a scheduler
-    // are half a period apart, so one computes while the other waits for its MMAs, loads and stores
+    // ------------------------------------------------------------------ score rows (warps 0..7): thread = (key, column half)
     const int q = warp_idx & 3;          // tensor-memory lane quarter
-    const int half = warp_idx >> 2;      // step buffer; in the epilogue the 64-column box
+    const int half = warp_idx >> 2;      // queries [64 * half, 64 * half + 64) of the block
     const int r = q * 32 + static_cast<int>(lane);
     const uint32_t lane_field = static_cast<uint32_t>(q * 32) << 16;
-    const uint32_t t_buf = tmem_base + lane_field + half * 128;
-    int stage = half;                    // ring position of this group's next step (steps alternate between the groups)
-    uint32_t stage_phase = 0, items = 0, blocks = 0;
+    const uint32_t t_s = tmem_base + lane_field + C_ST + half * 64, t_dp = tmem_base + lane_field + C_DPT + half * 64;
+    uint32_t items = 0, g = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
-      int hz, blk, s_begin, s_end;
-      item_range(item, hz, blk, s_begin, s_end);
-      float m_i = 0.f, d_i = 0.f;
-      if (!DKDV) {
-        const int64_t my_row = static_cast<int64_t>(hz) * p.N_CTX + blk * AT_BM + r;
-        m_i = __ldg(p.lse2 + my_row);
-        d_i = __ldg(p.delta + my_row);
-      }
-      if (RES_TMEM) {
-        // group 0 copies Q, group 1 dO: each thread its row, 128 bf16 -> 64 columns (two values per column, the layout
-        // of an MMA A operand in tensor memory).  The previous item's MMAs have all completed (acc_full was observed)
-        ok = mbar_wait(res_full, items & 1u, ctx, SITE + 9);
+      const int hz = item / p.num_blk, n = item - hz * p.num_blk;
+      for (int m = p.causal ? n : 0; ok && m < p.num_blk; ++m, ++g) {
+        const uint32_t st = g & 1u;
+        const float* mvec = smem_vec + st * 256 + half * 64;
+        const bool diag = p.causal && m == n;
+        float pr[64];
+        // the M and delta vectors are read from shared memory below: observe their arrival directly
+        ok = mbar_wait(&q_full[st], (g >> 1) & 1u, ctx, 89);
         if (!ok) break;
-        const uint8_t* src = (half == 0 ? smem_res0 : smem_res1) + r * 128;
-        const uint32_t t_res = tmem_base + lane_field + (half == 0 ? C_RES0 : C_RES1);
-#pragma unroll
-        for (int bx = 0; bx < 2; ++bx) {
-          uint32_t w[32];
-#pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            const uint4 v4 = *reinterpret_cast<const uint4*>(src + bx * AT_BOX_BYTES + ((ch ^ (r & 7)) << 4));
-            w[4 * ch] = v4.x; w[4 * ch + 1] = v4.y; w[4 * ch + 2] = v4.z; w[4 * ch + 3] = v4.w;
-          }
-          tmem_st_x32(t_res + bx * 32, w);
-        }
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(res_ready);
-      }
-      for (int sb = s_begin; ok && sb < s_end; ++sb, ++blocks) {
-        const bool diag = p.causal && sb == blk;
-        if (DKDV) {   // the step's M and delta vectors are read from shared memory below: observe their arrival directly
-          ok = mbar_wait(&st_full[stage], stage_phase, ctx, SITE + 8);
-          if (!ok) break;
-        }
-        ok = mbar_wait(&x_full[half], blocks & 1u, ctx, SITE + 6);
+        ok = mbar_wait(s_full, g & 1u, ctx, 90);
         if (!ok) break;
         tc_fence_after();
-        {
-          const float* vec = DKDV ? reinterpret_cast<const float*>(smem_stage + stage * BW_STAGE_BYTES + 2 * BW_SUB_TILE) : nullptr;
-          const int col0 = half * BW_SUB;               // the step's first score, as an index into the streamed block
-          if (diag) score_step<DKDV, true>(t_buf, vec, p.qk_scale, m_i, d_i, col0, r);
-          else score_step<DKDV, false>(t_buf, vec, p.qk_scale, m_i, d_i, col0, r);
-        }
+        if (diag) score_phase1<true, true>(t_s, mvec, p.qk_scale, 0.f, half * 64, r, pr);
+        else score_phase1<true, false>(t_s, mvec, p.qk_scale, 0.f, half * 64, r, pr);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p1_ready);      // S^T is in registers: the next block's S^T may overwrite it
+        ok = mbar_wait(dp_full, g & 1u, ctx, 91);
+        if (!ok) break;
+        tc_fence_after();
+        score_phase2<true>(t_dp, t_dp, mvec + 128, 0.f, pr);   // dS^T over the first 32 of the thread's dP^T columns
+        store_bf16_64(t_dp + 32, pr);                          // P^T over the other 32 (all 64 have been read)
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_ready[half]);
-        stage += 2;                       // BW_NSTAGE is even: a group stays on stages of its own parity
-        if (stage >= BW_NSTAGE) { stage -= BW_NSTAGE; stage_phase ^= 1u; }
+        if (lane == 0) mbar_arrive(p2_ready);
       }
       if (!ok) break;
-      // ---- epilogue: accumulators -> x scale -> bf16 -> staging in the resident tiles (no longer needed) -> TMA store
-      ok = mbar_wait(acc_full, items & 1u, ctx, SITE + 7);
+      // ---- epilogue: dV and sm_scale * dK -> bf16 -> staging in the K / V tiles (no longer needed) -> TMA store
+      ok = mbar_wait(acc_full, items & 1u, ctx, 92);
       if (!ok) break;
       tc_fence_after();
-      store_acc(tmem_base + lane_field + C_ACC0, DKDV ? 1.0f : p.sm_scale, smem_res0, r, half);
-      if (DKDV) store_acc(tmem_base + lane_field + C_ACC1, p.sm_scale, smem_res1, r, half);
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
+      epilogue_store(tmem_base + lane_field + C_DV, 1.0f, smem_k, &tmap_dv, true, tmem_base + lane_field + C_DK, p.sm_scale,
+                     smem_v, &tmap_dk, r, q, half, hz * p.N_CTX + n * AT_BN + q * 32, lane, acc_empty, res_empty);
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  drain_after_abort(abort_smem);
+  tc_fence_before();
+  __syncthreads();
+  if (warp_idx == BW_WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// dQ: one item = (batch*head, query block m); Q, dO resident; the key blocks n stream (n <= m when causal).
+// Rows of the score tiles are queries: S = Q K^T (two buffers), dP = dO V^T, dQ += dS K.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int DQ_NK = 3, DQ_NV = 2;                                   // K lives until dQ += dS K, V only until dP
+constexpr int DQ_K_OFF = 2 * BW_TILE_BYTES;                           // after the resident Q and dO tiles
+constexpr int DQ_V_OFF = DQ_K_OFF + DQ_NK * BW_TILE_BYTES;
+constexpr int DQ_BAR_OFF = DQ_V_OFF + DQ_NV * BW_TILE_BYTES;
+constexpr int DQ_NBAR = 2 + 2 * DQ_NK + 2 * DQ_NV + 6;
+constexpr int DQ_SMEM_TOTAL = DQ_BAR_OFF + DQ_NBAR * 8 + 16 + 1024;
+static_assert(DQ_SMEM_TOTAL <= 232448, "attention backward (dQ) shared memory budget exceeded");
+
+__global__ void __launch_bounds__(BW_THREADS, 1)
+attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                           const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                           const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
+  constexpr uint32_t IDESC_SS = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);
+  constexpr uint32_t IDESC_TS = umma_idesc_bf16_f32(AT_BM, BW_D, 0, 1);
+  constexpr uint32_t C_S = 0 /* buffer 1 at 128 */, C_DP = 256, C_DQ = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_q = smem;
+  uint8_t* smem_do = smem + BW_TILE_BYTES;
+  uint8_t* smem_k = smem + DQ_K_OFF;
+  uint8_t* smem_v = smem + DQ_V_OFF;
+  uint64_t* res_full = reinterpret_cast<uint64_t*>(smem + DQ_BAR_OFF);
+  uint64_t* res_empty = res_full + 1;
+  uint64_t* k_full = res_empty + 1;
+  uint64_t* k_empty = k_full + DQ_NK;                                    // [slot] released after dQ += dS K
+  uint64_t* v_full = k_empty + DQ_NK;
+  uint64_t* v_empty = v_full + DQ_NV;                                    // [slot] released after dP = dO V^T
+  uint64_t* s_full = v_empty + DQ_NV;                                    // [buffer] S is in tensor memory
+  uint64_t* dp_full = s_full + 2;                                        // dP is in tensor memory
+  uint64_t* p_ready = dp_full + 1;                                       // dS written over S; S and dP consumed (8 warps)
+  uint64_t* acc_full = p_ready + 1;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  uint32_t* abort_smem = tmem_ptr_smem + 1;
+
+  const int warp_idx = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  WaitCtx ctx{abort_smem, p.status};
+
+  if (threadIdx.x == 0) {
+    mbar_init(res_full, 1);
+    mbar_init(res_empty, BW_SCORE_WARPS);
+    for (int s = 0; s < DQ_NK; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < DQ_NV; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_ready, BW_SCORE_WARPS);
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, BW_SCORE_WARPS);
+    *abort_smem = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_do);
+  }
+  if (warp_idx == BW_WARP_MMA) {
+    tmem_alloc(tmem_ptr_smem, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  // causal items take m + 1 blocks: hand out the long ones first
+  auto item_block = [&](int item, int& hz, int& m) {
+    hz = item / p.num_blk;
+    m = item - hz * p.num_blk;
+    if (p.causal) m = p.num_blk - 1 - m;
+  };
+
+  // Every role counts the blocks it has walked in `g`: S buffer g % 2, K slot g % 3, V slot g % 2.
+  if (warp_idx == BW_WARP_TMA) {
+    // ------------------------------------------------------------------ TMA producer
+    uint32_t items = 0, g = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
+      int hz, m;
+      item_block(item, hz, m);
+      const int row_base = hz * p.N_CTX;
+      ok = mbar_wait(res_empty, (items & 1u) ^ 1u, ctx, 100);
+      if (!ok) break;
       if (lane == 0) {
-        mbar_arrive(acc_empty);
-        const int y = hz * p.N_CTX + blk * AT_BM + q * 32;
-        tma_store_2d(&tmap_out0, smem_res0 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
-        if (DKDV) tma_store_2d(&tmap_out1, smem_res1 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
-        tma_store_commit();
-        tma_store_wait_read<0>();
-        mbar_arrive(res_empty);
+        mbar_expect_tx(res_full, 2 * BW_TILE_BYTES);
+        load_tile(smem_q, &tmap_q, res_full, row_base + m * AT_BM);
+        load_tile(smem_do, &tmap_do, res_full, row_base + m * AT_BM);
       }
       __syncwarp();
+      const int n_end = p.causal ? m + 1 : p.num_blk;
+      for (int n = 0; ok && n < n_end; ++n, ++g) {
+        const uint32_t ks = g % DQ_NK, kph = (g / DQ_NK) & 1u, vs = g % DQ_NV, vph = (g / DQ_NV) & 1u;
+        ok = mbar_wait(&k_empty[ks], kph ^ 1u, ctx, 101);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(&k_full[ks], BW_TILE_BYTES);
+          load_tile(smem_k + ks * BW_TILE_BYTES, &tmap_k, &k_full[ks], row_base + n * AT_BN);
+        }
+        __syncwarp();
+        ok = mbar_wait(&v_empty[vs], vph ^ 1u, ctx, 102);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(&v_full[vs], BW_TILE_BYTES);
+          load_tile(smem_v + vs * BW_TILE_BYTES, &tmap_v, &v_full[vs], row_base + n * AT_BN);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp_idx == BW_WARP_MMA) {
+    // ------------------------------------------------------------------ MMA issuer
+    uint32_t items = 0, g = 0;
+    bool ok = true;
+    const uint64_t q_desc = umma_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
+    const uint64_t do_desc = umma_smem_desc_sw128(smem_u32(smem_do), 16, 1024);
+    // S = Q K^T of block gg into buffer gg % 2; dP = dO V^T of block gg (each waits for its tile first)
+    auto issue_s = [&](uint32_t gg) -> bool {
+      const uint32_t ks = gg % DQ_NK;
+      if (!mbar_wait(&k_full[ks], (gg / DQ_NK) & 1u, ctx, 103)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint64_t kd = umma_smem_desc_sw128(smem_u32(smem_k + ks * BW_TILE_BYTES), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < BW_D / 16; ++kk)
+          umma_ss(tmem_base + C_S + (gg & 1u) * 128, q_desc + koff_cols(kk), kd + koff_cols(kk), IDESC_SS, kk > 0 ? 1u : 0u);
+        umma_commit(&s_full[gg & 1u]);
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_dp = [&](uint32_t gg) -> bool {
+      const uint32_t vs = gg % DQ_NV;
+      if (!mbar_wait(&v_full[vs], (gg / DQ_NV) & 1u, ctx, 104)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint64_t vd = umma_smem_desc_sw128(smem_u32(smem_v + vs * BW_TILE_BYTES), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < BW_D / 16; ++kk)
+          umma_ss(tmem_base + C_DP, do_desc + koff_cols(kk), vd + koff_cols(kk), IDESC_SS, kk > 0 ? 1u : 0u);
+        umma_commit(dp_full);
+        umma_commit(&v_empty[vs]);
+      }
+      __syncwarp();
+      return true;
+    };
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
+      int hz, m;
+      item_block(item, hz, m);
+      const int nb = p.causal ? m + 1 : p.num_blk;
+      ok = mbar_wait(res_full, items & 1u, ctx, 105);
+      if (!ok) break;
+      ok = issue_s(g) && issue_dp(g);
+      if (ok && nb > 1) ok = issue_s(g + 1);
+      for (int j = 0; ok && j < nb; ++j, ++g) {
+        // all warps have read S and dP of block g and written dS over S
+        ok = mbar_wait(p_ready, g & 1u, ctx, 106);
+        if (!ok) break;
+        if (j == 0) {
+          ok = mbar_wait(acc_empty, (items & 1u) ^ 1u, ctx, 107);
+          if (!ok) break;
+        }
+        if (j + 1 < nb) {   // first what the score warps wait for next
+          ok = issue_dp(g + 1);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          // dQ += dS K: A = dS (bf16 over S of buffer g % 2), contraction over the keys
+          const uint32_t ks = g % DQ_NK;
+          const uint64_t kn = umma_smem_desc_sw128(smem_u32(smem_k + ks * BW_TILE_BYTES), AT_BOX_BYTES, 1024);
+#pragma unroll
+          for (int kk = 0; kk < AT_BN / 16; ++kk)
+            umma_ts(tmem_base + C_DQ, tmem_base + C_S + (g & 1u) * 128 + bf16_col(kk), kn + koff_rows(kk), IDESC_TS,
+                    (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&k_empty[ks]);
+          if (j == nb - 1) umma_commit(acc_full);
+        }
+        __syncwarp();
+        if (j + 2 < nb) {   // the freed buffer takes the S after next (after the MMAs above have read dS: in order)
+          ok = issue_s(g + 2);
+          if (!ok) break;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ score rows (warps 0..7): thread = (query, column half)
+    const int q = warp_idx & 3;
+    const int half = warp_idx >> 2;      // keys [64 * half, 64 * half + 64) of the block
+    const int r = q * 32 + static_cast<int>(lane);
+    const uint32_t lane_field = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t t_dp = tmem_base + lane_field + C_DP + half * 64;
+    uint32_t items = 0, g = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
+      int hz, m;
+      item_block(item, hz, m);
+      const int64_t my_row = static_cast<int64_t>(hz) * p.N_CTX + m * AT_BM + r;
+      const float m_i = __ldg(p.lse2 + my_row), d_i = __ldg(p.delta + my_row);
+      const int n_end = p.causal ? m + 1 : p.num_blk;
+      for (int n = 0; ok && n < n_end; ++n, ++g) {
+        const uint32_t t_s = tmem_base + lane_field + C_S + (g & 1u) * 128 + half * 64;
+        const bool diag = p.causal && n == m;
+        float pr[64];
+        ok = mbar_wait(&s_full[g & 1u], (g >> 1) & 1u, ctx, 108);
+        if (!ok) break;
+        tc_fence_after();
+        if (diag) score_phase1<false, true>(t_s, nullptr, p.qk_scale, m_i, half * 64, r, pr);
+        else score_phase1<false, false>(t_s, nullptr, p.qk_scale, m_i, half * 64, r, pr);
+        ok = mbar_wait(dp_full, g & 1u, ctx, 109);
+        if (!ok) break;
+        tc_fence_after();
+        score_phase2<false>(t_dp, t_s, nullptr, d_i, pr);      // dS over the first 32 of the thread's S columns
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready);
+      }
+      if (!ok) break;
+      // ---- epilogue: sm_scale * dQ -> bf16 -> staging in the Q tile -> TMA store
+      ok = mbar_wait(acc_full, items & 1u, ctx, 110);
+      if (!ok) break;
+      tc_fence_after();
+      epilogue_store(tmem_base + lane_field + C_DQ, p.sm_scale, smem_q, &tmap_dq, false, 0, 0.f, nullptr, nullptr, r, q, half,
+                     hz * p.N_CTX + m * AT_BM + q * 32, lane, acc_empty, res_empty);
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
@@ -536,16 +773,10 @@ int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   const uint64_t rows = static_cast<uint64_t>(zh) * a.N_CTX;
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   int rc;
-  // resident tiles: boxes of 128 rows; streamed half-tiles: boxes of 64 rows; results: boxes of 32 rows (one warp's)
-  CUtensorMap tq_s, tk_s, tv_s, tdo_s;
   if ((rc = make_tmap_bf16_2d(&tq, a.q, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tk, a.k, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tv, a.v, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tdo, a.d_o, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tq_s, a.q, BW_D, rows, BW_D, 64, BW_SUB)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tk_s, a.k, BW_D, rows, BW_D, 64, BW_SUB)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tv_s, a.v, BW_D, rows, BW_D, 64, BW_SUB)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdo_s, a.d_o, BW_D, rows, BW_D, 64, BW_SUB)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tdq, a.dq, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tdk, a.dk, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
   if ((rc = make_tmap_bf16_2d(&tdv, a.dv, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
@@ -571,15 +802,15 @@ int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   B200K_CHECK_LAUNCH("attn_bwd_delta_kernel");
 
   const int grid = p.num_items < dev->sm_count ? p.num_items : dev->sm_count;
-  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BW_SMEM_TOTAL));
-  attn_bwd_tcgen05_kernel<true><<<grid, BW_THREADS, BW_SMEM_TOTAL, stream>>>(tk, tv, tq_s, tdo_s, tdv, tdk, p);
+  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM_TOTAL));
+  attn_bwd_dkdv_tcgen05_kernel<<<grid, BW_THREADS, KV_SMEM_TOTAL, stream>>>(tq, tk, tv, tdo, tdk, tdv, p);
   count_launch();
-  B200K_CHECK_LAUNCH("attn_bwd_tcgen05_kernel<dK, dV>");
+  B200K_CHECK_LAUNCH("attn_bwd_dkdv_tcgen05_kernel");
 
-  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BW_SMEM_TOTAL));
-  attn_bwd_tcgen05_kernel<false><<<grid, BW_THREADS, BW_SMEM_TOTAL, stream>>>(tq, tdo, tk_s, tv_s, tdq, tdq, p);
+  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dq_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM_TOTAL));
+  attn_bwd_dq_tcgen05_kernel<<<grid, BW_THREADS, DQ_SMEM_TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
   count_launch();
-  B200K_CHECK_LAUNCH("attn_bwd_tcgen05_kernel<dQ>");
+  B200K_CHECK_LAUNCH("attn_bwd_dq_tcgen05_kernel");
   return B200K_OK;
 }
 
