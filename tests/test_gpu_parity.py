@@ -751,6 +751,39 @@ def test_attention_backward_cabi_writes_only_its_outputs():
     assert float((delta - ref_delta).abs().max()) <= 1e-4 * float(ref_delta.abs().max()) + 1e-5
 
 
+def test_attention_backward_in_a_cuda_graph():
+    # forward + backward recorded once and replayed on new data: neither allocates inside the library nor synchronises
+    Z, H, S, D = 1, 2, 384, 128
+    scale = D ** -0.5
+    q, k, v = (t.cuda() for t in gi.attn_inputs(Z, H, S, D, seed=37))
+    d_o = _d_o(Z, H, S, D, seed=38).cuda()
+
+    def step():
+        o, m = ops.attention_with_lse(q, k, v, True, scale)
+        return ops.attention_backward(q, k, v, o, m, d_o, True, scale)
+
+    want1 = [t.clone() for t in step()]
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = step()
+    graph.replay()
+    torch.cuda.synchronize()
+    for got, want in zip(outs, want1):
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    q2, k2, v2 = gi.attn_inputs(Z, H, S, D, seed=39)
+    for dst, src in ((q, q2), (k, k2), (v, v2), (d_o, _d_o(Z, H, S, D, seed=40))):
+        dst.copy_(src)
+    graph.replay()
+    torch.cuda.synchronize()
+    got2 = [t.clone() for t in outs]
+    want2 = step()
+    torch.cuda.synchronize()
+    for got, want in zip(got2, want2):
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert ops.device_status() == 0
+
+
 def test_attention_backward_rejects_unsupported():
     q = torch.zeros(1, 1, 256, 64, dtype=torch.bfloat16, device="cuda")
     m = torch.zeros(1, 1, 256, device="cuda")
