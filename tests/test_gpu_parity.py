@@ -661,11 +661,12 @@ def _autograd_truth(q, k, v, d_o, causal, scale):
     return qf.grad, kf.grad, vf.grad
 
 
-@pytest.mark.parametrize("Z,H,S,causal", [(1, 1, 128, False), (1, 1, 128, True), (1, 2, 256, False), (1, 3, 512, True),
-                                          (2, 2, 1024, False), (1, 2, 1024, True), (3, 5, 384, True)])
-def test_attention_backward_oracle(Z, H, S, causal):
+@pytest.mark.parametrize("Z,H,S,causal,D", [(1, 1, 128, False, 128), (1, 1, 128, True, 128), (1, 2, 256, False, 128),
+                                            (1, 3, 512, True, 128), (2, 2, 1024, False, 128), (1, 2, 1024, True, 128),
+                                            (3, 5, 384, True, 128), (1, 1, 128, True, 64), (2, 3, 512, False, 64),
+                                            (1, 4, 1024, True, 64), (3, 5, 384, True, 64)])
+def test_attention_backward_oracle(Z, H, S, causal, D):
     # dq, dk, dv against the CPU oracle (parity unpinned: the reference has no backward) and against fp32 autograd
-    D = 128
     scale = D ** -0.5
     q, k, v = gi.attn_inputs(Z, H, S, D, seed=32)
     d_o = _d_o(Z, H, S, D)
@@ -785,10 +786,10 @@ def test_attention_backward_in_a_cuda_graph():
 
 
 def test_attention_backward_rejects_unsupported():
-    q = torch.zeros(1, 1, 256, 64, dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros(1, 1, 256, 32, dtype=torch.bfloat16, device="cuda")
     m = torch.zeros(1, 1, 256, device="cuda")
     with pytest.raises(NotImplementedError):
-        ops.attention_backward(q, q, q, q, m, q, False, 0.1)          # HEAD_DIM 64
+        ops.attention_backward(q, q, q, q, m, q, False, 0.1)          # HEAD_DIM 32
     q = torch.zeros(1, 1, 192, 128, dtype=torch.bfloat16, device="cuda")
     m = torch.zeros(1, 1, 192, device="cuda")
     with pytest.raises(NotImplementedError):

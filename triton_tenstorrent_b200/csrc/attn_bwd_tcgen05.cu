@@ -45,11 +45,11 @@
 
 namespace b200k {
 
-constexpr int BW_D = 128;
 constexpr int BW_THREADS = 320;
 constexpr int BW_SCORE_WARPS = 8;
 constexpr int BW_WARP_TMA = 8, BW_WARP_MMA = 9;
-constexpr int BW_TILE_BYTES = AT_BM * BW_D * 2;       // 32 KB: two boxes of 128 rows x 64 columns
+// A tile is 128 rows x HEAD_DIM columns of bf16: HEAD_DIM / 64 TMA boxes of 128 rows x 64 columns (16 KB each).
+constexpr int bw_tile_bytes(int D) { return AT_BM * D * 2; }
 
 struct BwdParams {
   int ZH, N_CTX, num_blk;
@@ -63,19 +63,22 @@ struct BwdParams {
 };
 
 // ---------------------------------------------------------------------------------------------------------------
-// delta = rowsum(O * dO): one warp per row of 128 bf16 values
+// delta = rowsum(O * dO): one warp per row of D bf16 values (D / 4 lanes load four values each)
 // ---------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const uint2* __restrict__ o, const uint2* __restrict__ d_o,
-                                                             float* __restrict__ delta, int64_t rows) {
+                                                             float* __restrict__ delta, int64_t rows, int d4) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   for (int64_t row = warp; row < rows; row += nwarps) {
-    const uint2 a = __ldg(o + row * 32 + lane), b = __ldg(d_o + row * 32 + lane);   // four bf16 each
-    float s = bf16_bits_to_f32(a.x & 0xFFFFu) * bf16_bits_to_f32(b.x & 0xFFFFu);
-    s = fmaf(bf16_bits_to_f32(a.x >> 16), bf16_bits_to_f32(b.x >> 16), s);
-    s = fmaf(bf16_bits_to_f32(a.y & 0xFFFFu), bf16_bits_to_f32(b.y & 0xFFFFu), s);
-    s = fmaf(bf16_bits_to_f32(a.y >> 16), bf16_bits_to_f32(b.y >> 16), s);
+    float s = 0.f;
+    if (lane < d4) {
+      const uint2 a = __ldg(o + row * d4 + lane), b = __ldg(d_o + row * d4 + lane);   // four bf16 each
+      s = bf16_bits_to_f32(a.x & 0xFFFFu) * bf16_bits_to_f32(b.x & 0xFFFFu);
+      s = fmaf(bf16_bits_to_f32(a.x >> 16), bf16_bits_to_f32(b.x >> 16), s);
+      s = fmaf(bf16_bits_to_f32(a.y & 0xFFFFu), bf16_bits_to_f32(b.y & 0xFFFFu), s);
+      s = fmaf(bf16_bits_to_f32(a.y >> 16), bf16_bits_to_f32(b.y >> 16), s);
+    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
     if (lane == 0) delta[row] = s;
@@ -96,10 +99,11 @@ __device__ __forceinline__ uint64_t koff_cols(int kk) {
 }
 __device__ __forceinline__ uint64_t koff_rows(int kk) { return static_cast<uint64_t>((kk * 2048) >> 4); }
 
-// One 128 x 128 tile: two TMA boxes.
+// One 128 x D tile: D / 64 TMA boxes.
+template <int D>
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row) {
-  tma_load_2d(dst, m, bar, 0, row);
-  tma_load_2d(dst + AT_BOX_BYTES, m, bar, 64, row);
+#pragma unroll
+  for (int bx = 0; bx < D / 64; ++bx) tma_load_2d(dst + bx * AT_BOX_BYTES, m, bar, bx * 64, row);
 }
 
 // Tensor-memory column (relative to a 128-column fp32 tile) of the bf16 operand's k-step kk (16 values = 8 columns):
@@ -224,18 +228,23 @@ __device__ __forceinline__ void score_phase2(uint32_t t_dp, uint32_t t_dst, cons
 __device__ __forceinline__ void epilogue_store(uint32_t t_acc0, float scale0, uint8_t* stage0, const CUtensorMap* out0,
                                                bool two, uint32_t t_acc1, float scale1, uint8_t* stage1,
                                                const CUtensorMap* out1, int r, int q, int half, int y, uint32_t lane,
-                                               uint64_t* acc_empty, uint64_t* res_empty) {
-  store_acc(t_acc0, scale0, stage0, r, half);
-  if (two) store_acc(t_acc1, scale1, stage1, r, half);
+                                               uint64_t* acc_empty, uint64_t* res_empty, bool active) {
+  // HEAD_DIM 128: each half stores its 64-column box; HEAD_DIM 64: the one box is stored by the first half alone
+  if (active) {
+    store_acc(t_acc0, scale0, stage0, r, half);
+    if (two) store_acc(t_acc1, scale1, stage1, r, half);
+  }
   tc_fence_before();
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0) {
     mbar_arrive(acc_empty);
-    tma_store_2d(out0, stage0 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
-    if (two) tma_store_2d(out1, stage1 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
-    tma_store_commit();
-    tma_store_wait_read<0>();
+    if (active) {
+      tma_store_2d(out0, stage0 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
+      if (two) tma_store_2d(out1, stage1 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
+      tma_store_commit();
+      tma_store_wait_read<0>();
+    }
     mbar_arrive(res_empty);
   }
   __syncwarp();
@@ -246,14 +255,14 @@ __device__ __forceinline__ void epilogue_store(uint32_t t_acc0, float scale0, ui
 // Rows of the score tiles are keys: S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int KV_NSTAGE = 2;
-constexpr int KV_Q_OFF = 2 * BW_TILE_BYTES;                           // after the resident K and V tiles
-constexpr int KV_DO_OFF = KV_Q_OFF + KV_NSTAGE * BW_TILE_BYTES;
-constexpr int KV_VEC_OFF = KV_DO_OFF + KV_NSTAGE * BW_TILE_BYTES;     // per stage 128 M values, 128 delta values
-constexpr int KV_BAR_OFF = KV_VEC_OFF + KV_NSTAGE * 1024;
 constexpr int KV_NBAR = 2 + 4 * KV_NSTAGE + 6;
-constexpr int KV_SMEM_TOTAL = KV_BAR_OFF + KV_NBAR * 8 + 16 + 1024;
-static_assert(KV_SMEM_TOTAL <= 232448, "attention backward (dK/dV) shared memory budget exceeded");
+// shared memory: K, V | Q stages | dO stages | per stage 128 M values and 128 delta values | barriers
+constexpr int kv_vec_off(int D) { return (2 + 2 * KV_NSTAGE) * bw_tile_bytes(D); }
+constexpr int kv_bar_off(int D) { return kv_vec_off(D) + KV_NSTAGE * 1024; }
+constexpr int kv_smem_total(int D) { return kv_bar_off(D) + KV_NBAR * 8 + 16 + 1024; }
+static_assert(kv_smem_total(128) <= 232448, "attention backward (dK/dV) shared memory budget exceeded");
 
+template <int BW_D>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -261,7 +270,10 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
                              const BwdParams p) {
   constexpr uint32_t IDESC_SS = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);   // both operands K-major
   constexpr uint32_t IDESC_TS = umma_idesc_bf16_f32(AT_BM, BW_D, 0, 1);    // A in tensor memory, B MN-major
-  constexpr uint32_t C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 384;
+  constexpr uint32_t C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 256 + BW_D;
+  constexpr int BW_TILE_BYTES = bw_tile_bytes(BW_D);
+  constexpr int KV_Q_OFF = 2 * BW_TILE_BYTES, KV_DO_OFF = KV_Q_OFF + KV_NSTAGE * BW_TILE_BYTES;
+  constexpr int KV_VEC_OFF = kv_vec_off(BW_D), KV_BAR_OFF = kv_bar_off(BW_D);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -333,8 +345,8 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       if (!ok) break;
       if (lane == 0) {
         mbar_expect_tx(res_full, 2 * BW_TILE_BYTES);
-        load_tile(smem_k, &tmap_k, res_full, row_base + n * AT_BN);
-        load_tile(smem_v, &tmap_v, res_full, row_base + n * AT_BN);
+        load_tile<BW_D>(smem_k, &tmap_k, res_full, row_base + n * AT_BN);
+        load_tile<BW_D>(smem_v, &tmap_v, res_full, row_base + n * AT_BN);
       }
       __syncwarp();
       for (int m = p.causal ? n : 0; ok && m < p.num_blk; ++m, ++g) {
@@ -344,7 +356,7 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&q_full[st], BW_TILE_BYTES + 1024);
-          load_tile(smem_q + st * BW_TILE_BYTES, &tmap_q, &q_full[st], row);
+          load_tile<BW_D>(smem_q + st * BW_TILE_BYTES, &tmap_q, &q_full[st], row);
           bulk_load_1d(smem_vec + st * 256, p.lse2 + row, 512, &q_full[st]);
           bulk_load_1d(smem_vec + st * 256 + 128, p.delta + row, 512, &q_full[st]);
         }
@@ -353,7 +365,7 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&do_full[st], BW_TILE_BYTES);
-          load_tile(smem_do + st * BW_TILE_BYTES, &tmap_do, &do_full[st], row);
+          load_tile<BW_D>(smem_do + st * BW_TILE_BYTES, &tmap_do, &do_full[st], row);
         }
         __syncwarp();
       }
@@ -483,7 +495,8 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       if (!ok) break;
       tc_fence_after();
       epilogue_store(tmem_base + lane_field + C_DV, 1.0f, smem_k, &tmap_dv, true, tmem_base + lane_field + C_DK, p.sm_scale,
-                     smem_v, &tmap_dk, r, q, half, hz * p.N_CTX + n * AT_BN + q * 32, lane, acc_empty, res_empty);
+                     smem_v, &tmap_dk, r, q, half, hz * p.N_CTX + n * AT_BN + q * 32, lane, acc_empty, res_empty,
+                     BW_D == 128 || half == 0);
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
@@ -504,13 +517,13 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
 // Rows of the score tiles are queries: S = Q K^T (two buffers), dP = dO V^T, dQ += dS K.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int DQ_NK = 3, DQ_NV = 2;                                   // K lives until dQ += dS K, V only until dP
-constexpr int DQ_K_OFF = 2 * BW_TILE_BYTES;                           // after the resident Q and dO tiles
-constexpr int DQ_V_OFF = DQ_K_OFF + DQ_NK * BW_TILE_BYTES;
-constexpr int DQ_BAR_OFF = DQ_V_OFF + DQ_NV * BW_TILE_BYTES;
 constexpr int DQ_NBAR = 2 + 2 * DQ_NK + 2 * DQ_NV + 6;
-constexpr int DQ_SMEM_TOTAL = DQ_BAR_OFF + DQ_NBAR * 8 + 16 + 1024;
-static_assert(DQ_SMEM_TOTAL <= 232448, "attention backward (dQ) shared memory budget exceeded");
+// shared memory: Q, dO | K slots | V slots | barriers
+constexpr int dq_bar_off(int D) { return (2 + DQ_NK + DQ_NV) * bw_tile_bytes(D); }
+constexpr int dq_smem_total(int D) { return dq_bar_off(D) + DQ_NBAR * 8 + 16 + 1024; }
+static_assert(dq_smem_total(128) <= 232448, "attention backward (dQ) shared memory budget exceeded");
 
+template <int BW_D>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -518,6 +531,8 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   constexpr uint32_t IDESC_SS = umma_idesc_bf16_f32(AT_BM, AT_BN, 0, 0);
   constexpr uint32_t IDESC_TS = umma_idesc_bf16_f32(AT_BM, BW_D, 0, 1);
   constexpr uint32_t C_S = 0 /* buffer 1 at 128 */, C_DP = 256, C_DQ = 384;
+  constexpr int BW_TILE_BYTES = bw_tile_bytes(BW_D);
+  constexpr int DQ_K_OFF = 2 * BW_TILE_BYTES, DQ_V_OFF = DQ_K_OFF + DQ_NK * BW_TILE_BYTES, DQ_BAR_OFF = dq_bar_off(BW_D);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -596,8 +611,8 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       if (!ok) break;
       if (lane == 0) {
         mbar_expect_tx(res_full, 2 * BW_TILE_BYTES);
-        load_tile(smem_q, &tmap_q, res_full, row_base + m * AT_BM);
-        load_tile(smem_do, &tmap_do, res_full, row_base + m * AT_BM);
+        load_tile<BW_D>(smem_q, &tmap_q, res_full, row_base + m * AT_BM);
+        load_tile<BW_D>(smem_do, &tmap_do, res_full, row_base + m * AT_BM);
       }
       __syncwarp();
       const int n_end = p.causal ? m + 1 : p.num_blk;
@@ -607,14 +622,14 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&k_full[ks], BW_TILE_BYTES);
-          load_tile(smem_k + ks * BW_TILE_BYTES, &tmap_k, &k_full[ks], row_base + n * AT_BN);
+          load_tile<BW_D>(smem_k + ks * BW_TILE_BYTES, &tmap_k, &k_full[ks], row_base + n * AT_BN);
         }
         __syncwarp();
         ok = mbar_wait(&v_empty[vs], vph ^ 1u, ctx, 102);
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&v_full[vs], BW_TILE_BYTES);
-          load_tile(smem_v + vs * BW_TILE_BYTES, &tmap_v, &v_full[vs], row_base + n * AT_BN);
+          load_tile<BW_D>(smem_v + vs * BW_TILE_BYTES, &tmap_v, &v_full[vs], row_base + n * AT_BN);
         }
         __syncwarp();
       }
@@ -733,7 +748,7 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       if (!ok) break;
       tc_fence_after();
       epilogue_store(tmem_base + lane_field + C_DQ, p.sm_scale, smem_q, &tmap_dq, false, 0, 0.f, nullptr, nullptr, r, q, half,
-                     hz * p.N_CTX + m * AT_BM + q * 32, lane, acc_empty, res_empty);
+                     hz * p.N_CTX + m * AT_BM + q * 32, lane, acc_empty, res_empty, BW_D == 128 || half == 0);
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
@@ -752,12 +767,12 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
 // ---------------------------------------------------------------------------------------------------------------
 // Host
 // ---------------------------------------------------------------------------------------------------------------
-int attn_bwd_supported(int D, int N_CTX) { return (D == BW_D && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0; }
+int attn_bwd_supported(int D, int N_CTX) { return ((D == 64 || D == 128) && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0; }
 
 int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   if (a.Z <= 0 || a.H <= 0 || a.N_CTX <= 0) return set_error(B200K_ERR_INVALID_ARG, "attention backward: Z, H, N_CTX must be positive");
   if (!attn_bwd_supported(a.D, a.N_CTX))
-    return set_error(B200K_ERR_UNSUPPORTED, "attention backward: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 128, N_CTX a multiple of 128)", a.D, a.N_CTX);
+    return set_error(B200K_ERR_UNSUPPORTED, "attention backward: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 64 or 128, N_CTX a multiple of 128)", a.D, a.N_CTX);
   const void* ptrs[] = {a.q, a.k, a.v, a.o, a.d_o, a.lse2, a.dq, a.dk, a.dv, a.delta};
   for (const void* ptr : ptrs) {
     if (ptr == nullptr) return set_error(B200K_ERR_INVALID_ARG, "attention backward: null pointer");
@@ -773,13 +788,13 @@ int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   const uint64_t rows = static_cast<uint64_t>(zh) * a.N_CTX;
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   int rc;
-  if ((rc = make_tmap_bf16_2d(&tq, a.q, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tk, a.k, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tv, a.v, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdo, a.d_o, BW_D, rows, BW_D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdq, a.dq, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdk, a.dk, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdv, a.dv, BW_D, rows, BW_D, 64, 32)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tq, a.q, a.D, rows, a.D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tk, a.k, a.D, rows, a.D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tv, a.v, a.D, rows, a.D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tdo, a.d_o, a.D, rows, a.D, 64, AT_BM)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tdq, a.dq, a.D, rows, a.D, 64, 32)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tdk, a.dk, a.D, rows, a.D, 64, 32)) != 0) return rc;
+  if ((rc = make_tmap_bf16_2d(&tdv, a.dv, a.D, rows, a.D, 64, 32)) != 0) return rc;
 
   BwdParams p;
   p.ZH = static_cast<int>(zh);
@@ -797,20 +812,27 @@ int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   int delta_grid = static_cast<int>((delta_warps * 32 + 255) / 256);
   if (delta_grid > dev->sm_count * 8) delta_grid = dev->sm_count * 8;
   attn_bwd_delta_kernel<<<delta_grid, 256, 0, stream>>>(static_cast<const uint2*>(a.o), static_cast<const uint2*>(a.d_o),
-                                                        a.delta, static_cast<int64_t>(rows));
+                                                        a.delta, static_cast<int64_t>(rows), a.D / 4);
   count_launch();
   B200K_CHECK_LAUNCH("attn_bwd_delta_kernel");
 
   const int grid = p.num_items < dev->sm_count ? p.num_items : dev->sm_count;
-  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM_TOTAL));
-  attn_bwd_dkdv_tcgen05_kernel<<<grid, BW_THREADS, KV_SMEM_TOTAL, stream>>>(tq, tk, tv, tdo, tdk, tdv, p);
-  count_launch();
-  B200K_CHECK_LAUNCH("attn_bwd_dkdv_tcgen05_kernel");
-
-  B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dq_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM_TOTAL));
-  attn_bwd_dq_tcgen05_kernel<<<grid, BW_THREADS, DQ_SMEM_TOTAL, stream>>>(tq, tk, tv, tdo, tdq, p);
-  count_launch();
-  B200K_CHECK_LAUNCH("attn_bwd_dq_tcgen05_kernel");
+#define B200K_BWD_LAUNCH(DD)                                                                                                  \
+  do {                                                                                                                       \
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_tcgen05_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                          kv_smem_total(DD)));                                                               \
+    attn_bwd_dkdv_tcgen05_kernel<DD><<<grid, BW_THREADS, kv_smem_total(DD), stream>>>(tq, tk, tv, tdo, tdk, tdv, p);         \
+    count_launch();                                                                                                          \
+    B200K_CHECK_LAUNCH("attn_bwd_dkdv_tcgen05_kernel");                                                                      \
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dq_tcgen05_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                          dq_smem_total(DD)));                                                               \
+    attn_bwd_dq_tcgen05_kernel<DD><<<grid, BW_THREADS, dq_smem_total(DD), stream>>>(tq, tk, tv, tdo, tdq, p);                \
+    count_launch();                                                                                                          \
+    B200K_CHECK_LAUNCH("attn_bwd_dq_tcgen05_kernel");                                                                        \
+  } while (0)
+  if (a.D == 64) B200K_BWD_LAUNCH(64);
+  else B200K_BWD_LAUNCH(128);
+#undef B200K_BWD_LAUNCH
   return B200K_OK;
 }
 

@@ -462,7 +462,7 @@ def attention_multi(q, k, v, causal, sm_scale, out: torch.Tensor, remote_ptrs=()
 
 def attention_backward(q, k, v, o, M, d_o, causal, sm_scale):
     """(dq, dk, dv) from what the forward saved (q, k, v, o, M: examples/fused-attn/06-fused-attention.py:269) and the
-    gradient of o.  The reference has no backward kernel; this is the consumer of its saved tensors (HEAD_DIM 128,
+    gradient of o.  The reference has no backward kernel; this is the consumer of its saved tensors (HEAD_DIM 64 or 128,
     N_CTX a multiple of 128)."""
     if q.dim() != 4 or any(t.shape != q.shape for t in (k, v, o, d_o)):
         raise ValueError("attention_backward: q, k, v, o, d_o must be [Z, H, N_CTX, HEAD_DIM] with equal shapes")
@@ -474,7 +474,7 @@ def attention_backward(q, k, v, o, M, d_o, causal, sm_scale):
         raise ValueError("attention_backward: M must be [Z, H, N_CTX]")
     if not lib.b200k_attn_bwd_supported(D, N_CTX):
         raise NotImplementedError(f"attention backward: no sm_100a kernel for HEAD_DIM={D}, N_CTX={N_CTX} "
-                                  "(HEAD_DIM 128, N_CTX a multiple of 128)")
+                                  "(HEAD_DIM 64 or 128, N_CTX a multiple of 128)")
     qd, kd, vd, od, dod, Md = (_to_device(t).contiguous() for t in (q, k, v, o, d_o, M))
     dq, dk, dv = torch.empty_like(qd), torch.empty_like(qd), torch.empty_like(qd)
     delta = torch.empty((Z, H, N_CTX), device=qd.device, dtype=torch.float32)
