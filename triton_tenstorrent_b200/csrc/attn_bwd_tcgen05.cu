@@ -21,6 +21,7 @@
 //              staging, TMA store, one 64-column box per half
 //   warp 8     TMA producer
 //   warp 9     tensor-memory owner and tcgen05.mma issuer
+//   warps 10-11 no role; their registers go to the score warps (setmaxnreg: 208 per score thread, 88 for the others)
 // All MMAs are 128 x 128 x 16: a 128 x 64 x 16 instruction occupies the tensor pipe for 46 cycles against 64 (measured),
 // so stepping the streamed dimension by 64 rows (which would let two whole score buffers fit in tensor memory) makes the
 // score products cost 1.4 times as much; that version ran at 3.30 ms (Z=4, H=32, N_CTX=4096), the serial whole-block
@@ -45,7 +46,8 @@
 
 namespace b200k {
 
-constexpr int BW_THREADS = 320;
+constexpr int BW_THREADS = 384;           // warps 10 and 11 have no role: they only donate their registers
+constexpr int BW_REGS_SCORE = 208, BW_REGS_OTHER = 88;   // 8 x 32 x 208 + 4 x 32 x 88 = 384 x 168
 constexpr int BW_SCORE_WARPS = 8;
 constexpr int BW_WARP_TMA = 8, BW_WARP_MMA = 9;
 // A tile is 128 rows x HEAD_DIM columns of bf16: HEAD_DIM / 64 TMA boxes of 128 rows x 64 columns (16 KB each).
@@ -151,13 +153,15 @@ __device__ __forceinline__ void score_phase1(uint32_t t_s, const float* mvec, fl
   for (int k = 0; k < 4; ++k) {
     if (k + 1 < 4) tmem_ld_x16(t_s + (k + 1) * 16, in[(k + 1) & 1]);
     const uint32_t(&sk)[16] = in[k & 1];
+    float4 m4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
       const uint64_t s2 = pack_f32x2(__uint_as_float(sk[c]), __uint_as_float(sk[c + 1]));
       float x0, x1, p0, p1;
       if (COLS) {
-        const float2 m2 = *reinterpret_cast<const float2*>(mvec + k * 16 + c);
-        unpack_f32x2(fma_f32x2(s2, scale2, pack_f32x2(m2.x, m2.y)), x0, x1);     // M - s * qk_scale
+        if ((c & 2) == 0) m4 = *reinterpret_cast<const float4*>(mvec + k * 16 + c);   // one 16-byte load per four scores
+        const uint64_t m2 = (c & 2) == 0 ? pack_f32x2(m4.x, m4.y) : pack_f32x2(m4.z, m4.w);
+        unpack_f32x2(fma_f32x2(s2, scale2, m2), x0, x1);                          // M - s * qk_scale
         p0 = ex2_approx(-x0);
         p1 = ex2_approx(-x1);
         if (MASKED) {
@@ -180,17 +184,6 @@ __device__ __forceinline__ void score_phase1(uint32_t t_s, const float* mvec, fl
   }
 }
 
-// 64 fp32 values -> 32 columns of bf16 pairs at t_dst.
-__device__ __forceinline__ void store_bf16_64(uint32_t t_dst, const float (&v)[64]) {
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    uint32_t w[16];
-#pragma unroll
-    for (int c = 0; c < 16; ++c) w[c] = pack_bf16x2(v[g * 32 + 2 * c], v[g * 32 + 2 * c + 1]);
-    tmem_st_x16(t_dst + g * 16, w);
-  }
-}
-
 // Phase 2: dS = p * (dP - delta) for the thread's 64 values of dP at t_dp; bf16 result to the 32 columns at t_dst.
 template <bool COLS>
 __device__ __forceinline__ void score_phase2(uint32_t t_dp, uint32_t t_dst, const float* dvec, float d_i, const float (&pr)[64]) {
@@ -204,13 +197,15 @@ __device__ __forceinline__ void score_phase2(uint32_t t_dp, uint32_t t_dst, cons
   for (int k = 0; k < 4; ++k) {
     if (k + 1 < 4) tmem_ld_x16(t_dp + (k + 1) * 16, in[(k + 1) & 1]);
     const uint32_t(&dk)[16] = in[k & 1];
+    float4 dl4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < 16; c += 2) {
       const uint64_t d2 = pack_f32x2(__uint_as_float(dk[c]), __uint_as_float(dk[c + 1]));
       uint64_t t2;
       if (COLS) {
-        const float2 dl2 = *reinterpret_cast<const float2*>(dvec + k * 16 + c);
-        t2 = fma_f32x2(pack_f32x2(dl2.x, dl2.y), minus1, d2);                     // dP - delta
+        if ((c & 2) == 0) dl4 = *reinterpret_cast<const float4*>(dvec + k * 16 + c);
+        const uint64_t dl2 = (c & 2) == 0 ? pack_f32x2(dl4.x, dl4.y) : pack_f32x2(dl4.z, dl4.w);
+        t2 = fma_f32x2(dl2, minus1, d2);                                          // dP - delta
       } else {
         t2 = add_f32x2(d2, negd2);
       }
@@ -334,7 +329,9 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
 
   // Every role walks the same sequence of (item, block) and counts blocks in `g`: stage g % 2 (use g / 2 of it), and
   // the g-th completion of the single barriers.
-  if (warp_idx == BW_WARP_TMA) {
+  if (warp_idx >= BW_SCORE_WARPS) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BW_REGS_OTHER));   // all four warps, one instruction
+   if (warp_idx == BW_WARP_TMA) {
     // ------------------------------------------------------------------ TMA producer
     uint32_t items = 0, g = 0;
     bool ok = true;
@@ -452,7 +449,9 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         }
       }
     }
+   }  // warps 10 and 11 have no role
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(BW_REGS_SCORE));
     // ------------------------------------------------------------------ score rows (warps 0..7): thread = (key, column half)
     const int q = warp_idx & 3;          // tensor-memory lane quarter
     const int half = warp_idx >> 2;      // queries [64 * half, 64 * half + 64) of the block
@@ -479,11 +478,14 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p1_ready);      // S^T is in registers: the next block's S^T may overwrite it
+        uint32_t pp[32];                           // bf16 P^T, packed while dP^T is still on its way
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pp[c] = pack_bf16x2(pr[2 * c], pr[2 * c + 1]);
         ok = mbar_wait(dp_full, g & 1u, ctx, 91);
         if (!ok) break;
         tc_fence_after();
         score_phase2<true>(t_dp, t_dp, mvec + 128, 0.f, pr);   // dS^T over the first 32 of the thread's dP^T columns
-        store_bf16_64(t_dp + 32, pr);                          // P^T over the other 32 (all 64 have been read)
+        tmem_st_x32(t_dp + 32, pp);                            // P^T over the other 32 (all 64 have been read)
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -599,7 +601,9 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
   };
 
   // Every role counts the blocks it has walked in `g`: S buffer g % 2, K slot g % 3, V slot g % 2.
-  if (warp_idx == BW_WARP_TMA) {
+  if (warp_idx >= BW_SCORE_WARPS) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BW_REGS_OTHER));   // all four warps, one instruction
+   if (warp_idx == BW_WARP_TMA) {
     // ------------------------------------------------------------------ TMA producer
     uint32_t items = 0, g = 0;
     bool ok = true;
@@ -709,7 +713,9 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         }
       }
     }
+   }  // warps 10 and 11 have no role
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(BW_REGS_SCORE));
     // ------------------------------------------------------------------ score rows (warps 0..7): thread = (query, column half)
     const int q = warp_idx & 3;
     const int half = warp_idx >> 2;      // keys [64 * half, 64 * half + 64) of the block
