@@ -211,7 +211,8 @@ int b200k_attn_supported(int D, int N_CTX);
  * dS = P (d_o.v - delta); dk = sm_scale dS^T q; dq = sm_scale dS k), with P and dS rounded to bf16 where they enter a
  * tensor-core product and everything else in fp32.  delta_scratch: Z*H*N_CTX floats the caller provides (the
  * library allocates nothing).  D must be 64 or 128 and N_CTX a multiple of 128 (b200k_attn_bwd_supported tells); every
- * buffer 16-byte aligned.  Three kernel launches on `stream`, deterministic (no atomics).
+ * buffer 16-byte aligned; dq, dk, dv and delta_scratch must not overlap any input or each other (they are written
+ * while other CTAs still read q, k, v, o, d_o).  Three kernel launches on `stream`, deterministic (no atomics).
  */
 int b200k_attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
                         void* dq, void* dk, void* dv, float* delta_scratch, int Z, int H, int N_CTX, int D, int causal,

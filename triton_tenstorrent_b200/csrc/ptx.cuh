@@ -44,11 +44,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-#ifdef B200K_WAIT_POLL
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"   // pure polling: never parked by the hardware
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#endif
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
