@@ -135,30 +135,6 @@ __device__ __forceinline__ void store_acc(uint32_t t_acc, float scale, uint8_t* 
   }
 }
 
-// exp2 of two values on the FMA pipe (no ex2 unit): round to the nearest integer n with the 1.5 * 2^23 trick, 2^f for
-// f = x - n in [-0.5, 0.5] by the degree-4 Taylor polynomial of e^(f ln 2) (relative error <= 4e-5, far below the bf16
-// rounding that follows), n added to the exponent field as an integer.
-#ifndef B200K_BWD_EMULATED_PAIRS
-#define B200K_BWD_EMULATED_PAIRS 0   // of every 8 pairs of scores, this many take the polynomial instead of ex2
-#endif
-__device__ __forceinline__ void ex2_poly_x2(uint64_t x2, float& r0, float& r1) {
-  const uint64_t magic2 = pack_f32x2(12582912.0f, 12582912.0f), nmagic2 = pack_f32x2(-12582912.0f, -12582912.0f);
-  float x0, x1;
-  unpack_f32x2(x2, x0, x1);
-  x2 = pack_f32x2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
-  const uint64_t t2 = add_f32x2(x2, magic2);
-  const uint64_t f2 = fma_f32x2(add_f32x2(t2, nmagic2), pack_f32x2(-1.0f, -1.0f), x2);   // x - n
-  uint64_t p2 = fma_f32x2(f2, pack_f32x2(0.0096181291f, 0.0096181291f), pack_f32x2(0.0555041087f, 0.0555041087f));
-  p2 = fma_f32x2(p2, f2, pack_f32x2(0.2402265070f, 0.2402265070f));
-  p2 = fma_f32x2(p2, f2, pack_f32x2(0.6931471806f, 0.6931471806f));
-  p2 = fma_f32x2(p2, f2, pack_f32x2(1.0f, 1.0f));
-  float p0, p1, t0, t1;
-  unpack_f32x2(p2, p0, p1);
-  unpack_f32x2(t2, t0, t1);
-  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-}
-
 // Phase 1 of a thread's 64 scores at tensor-memory address t_s: p = exp2(qk_scale * s - M), fp32, into pr[].  Sixteen
 // columns at a time with the next sixteen in flight; pairs go through the packed fp32 instructions (each lane rounds
 // like the scalar form) because the issue slots beside the exponentials are what bounds this loop.
@@ -185,27 +161,17 @@ __device__ __forceinline__ void score_phase1(uint32_t t_s, const float* mvec, fl
       if (COLS) {
         if ((c & 2) == 0) m4 = *reinterpret_cast<const float4*>(mvec + k * 16 + c);   // one 16-byte load per four scores
         const uint64_t m2 = (c & 2) == 0 ? pack_f32x2(m4.x, m4.y) : pack_f32x2(m4.z, m4.w);
-        const uint64_t y2 = fma_f32x2(s2, scale2, m2);                            // M - s * qk_scale
-        if ((c >> 1) < B200K_BWD_EMULATED_PAIRS) {
-          ex2_poly_x2(fma_f32x2(y2, pack_f32x2(-1.0f, -1.0f), pack_f32x2(0.f, 0.f)), p0, p1);
-        } else {
-          unpack_f32x2(y2, x0, x1);
-          p0 = ex2_approx(-x0);
-          p1 = ex2_approx(-x1);
-        }
+        unpack_f32x2(fma_f32x2(s2, scale2, m2), x0, x1);                          // M - s * qk_scale
+        p0 = ex2_approx(-x0);
+        p1 = ex2_approx(-x1);
         if (MASKED) {
           if (col0 + k * 16 + c < r) p0 = 0.f;
           if (col0 + k * 16 + c + 1 < r) p1 = 0.f;
         }
       } else {
-        const uint64_t y2 = fma_f32x2(s2, scale2, negm2);
-        if ((c >> 1) < B200K_BWD_EMULATED_PAIRS) {
-          ex2_poly_x2(y2, p0, p1);
-        } else {
-          unpack_f32x2(y2, x0, x1);
-          p0 = ex2_approx(x0);
-          p1 = ex2_approx(x1);
-        }
+        unpack_f32x2(fma_f32x2(s2, scale2, negm2), x0, x1);
+        p0 = ex2_approx(x0);
+        p1 = ex2_approx(x1);
         if (MASKED) {
           if (col0 + k * 16 + c > r) p0 = 0.f;
           if (col0 + k * 16 + c + 1 > r) p1 = 0.f;
