@@ -210,7 +210,7 @@ int b200k_attn_supported(int D, int N_CTX);
  * reference's forward comes from (delta = rowsum(o * d_o); P recomputed as exp2(qk_scale * q.k - M); dv = P^T d_o;
  * dS = P (d_o.v - delta); dk = sm_scale dS^T q; dq = sm_scale dS k), with P and dS rounded to bf16 where they enter a
  * tensor-core product and everything else in fp32.  delta_scratch: Z*H*N_CTX floats the caller provides (the
- * library allocates nothing).  D must be 64 or 128 and N_CTX a multiple of 128 (b200k_attn_bwd_supported tells); every
+ * library allocates nothing).  D must be 64 or 128, N_CTX any length >= 1 (b200k_attn_bwd_supported tells); every
  * buffer 16-byte aligned; dq, dk, dv and delta_scratch must not overlap any input or each other (they are written
  * while other CTAs still read q, k, v, o, d_o).  Three kernel launches on `stream`, deterministic (no atomics).
  */

@@ -64,7 +64,7 @@ def test_argument_errors_before_any_device_work():
     assert lib.b200k_attn_supported(16, 128) == 1 and lib.b200k_attn_supported(256, 4096) == 1
     assert lib.b200k_attn_supported(48, 4096) == 0 and lib.b200k_attn_supported(128, 200) == 1 and lib.b200k_attn_supported(128, 0) == 0
     assert lib.b200k_attn_bwd_supported(128, 4096) == 1 and lib.b200k_attn_bwd_supported(64, 256) == 1
-    assert lib.b200k_attn_bwd_supported(32, 256) == 0 and lib.b200k_attn_bwd_supported(128, 192) == 0
+    assert lib.b200k_attn_bwd_supported(32, 256) == 0 and lib.b200k_attn_bwd_supported(128, 192) == 1 and lib.b200k_attn_bwd_supported(64, 0) == 0
     assert lib.b200k_attn_bwd_bf16(16, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 256, 256, 0, 0.1, None) == _lib.ERR_UNSUPPORTED
     assert lib.b200k_launch(b"no_such_kernel", 1, 1, 1, None, None, 0) == _lib.ERR_UNSUPPORTED
     assert lib.b200k_launch(b"add_kernel", 0, 1, 1, None, None, 0) == _lib.ERR_INVALID_ARG

@@ -664,7 +664,10 @@ def _autograd_truth(q, k, v, d_o, causal, scale):
 @pytest.mark.parametrize("Z,H,S,causal,D", [(1, 1, 128, False, 128), (1, 1, 128, True, 128), (1, 2, 256, False, 128),
                                             (1, 3, 512, True, 128), (2, 2, 1024, False, 128), (1, 2, 1024, True, 128),
                                             (3, 5, 384, True, 128), (1, 1, 128, True, 64), (2, 3, 512, False, 64),
-                                            (1, 4, 1024, True, 64), (3, 5, 384, True, 64)])
+                                            (1, 4, 1024, True, 64), (3, 5, 384, True, 64),
+                                            # N_CTX not a multiple of 128 (3-D tensor maps, zero-filled tails)
+                                            (1, 2, 200, False, 128), (2, 3, 333, True, 128), (1, 2, 96, True, 64),
+                                            (1, 1, 1000, False, 64), (2, 2, 129, True, 128), (1, 1, 7, False, 128)])
 def test_attention_backward_oracle(Z, H, S, causal, D):
     # dq, dk, dv against the CPU oracle (parity unpinned: the reference has no backward) and against fp32 autograd
     scale = D ** -0.5
@@ -723,9 +726,11 @@ def test_attention_backward_full_size_heads(causal):
             assert float((got[sl].float() - t).norm() / t.norm()) <= 1e-2, (name, z, h)
 
 
-def test_attention_backward_cabi_writes_only_its_outputs():
+@pytest.mark.parametrize("S,D", [(256, 128), (200, 128), (333, 64)])
+def test_attention_backward_cabi_writes_only_its_outputs(S, D):
     # straight through the C-ABI with dq, dk, dv inside canary-filled buffers: every element written, nothing around them
-    Z, H, S, D = 2, 3, 256, 128
+    # (the ragged lengths end inside a 128-row block of the last head: the rows past the end must not be stored)
+    Z, H = 2, 3
     scale = D ** -0.5
     q, k, v = (t.cuda() for t in gi.attn_inputs(Z, H, S, D, seed=36))
     d_o = _d_o(Z, H, S, D).cuda()
@@ -785,15 +790,29 @@ def test_attention_backward_in_a_cuda_graph():
     assert ops.device_status() == 0
 
 
+def test_attention_backward_single_key():
+    # N_CTX = 1: the softmax of one score is 1 whatever q and k are, so dv = dO and dq = dk = 0 (up to the rounding
+    # difference between the MMA's dO.V and the delta kernel's O.dO)
+    Z, H, D = 2, 3, 128
+    q, k, v = (t.cuda() for t in gi.attn_inputs(Z, H, 1, D, seed=45))
+    d_o = _d_o(Z, H, 1, D, seed=46).cuda()
+    o, m = ops.attention_with_lse(q, k, v, False, D ** -0.5)
+    dq, dk, dv = ops.attention_backward(q, k, v, o, m, d_o, False, D ** -0.5)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.equal(dv.view(torch.int16), d_o.view(torch.int16))
+    assert float(dq.float().abs().max()) <= 1e-4 and float(dk.float().abs().max()) <= 1e-4
+
+
 def test_attention_backward_rejects_unsupported():
     q = torch.zeros(1, 1, 256, 32, dtype=torch.bfloat16, device="cuda")
     m = torch.zeros(1, 1, 256, device="cuda")
     with pytest.raises(NotImplementedError):
         ops.attention_backward(q, q, q, q, m, q, False, 0.1)          # HEAD_DIM 32
-    q = torch.zeros(1, 1, 192, 128, dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros(1, 1, 192, 256, dtype=torch.bfloat16, device="cuda")
     m = torch.zeros(1, 1, 192, device="cuda")
     with pytest.raises(NotImplementedError):
-        ops.attention_backward(q, q, q, q, m, q, False, 0.1)          # N_CTX not a multiple of 128
+        ops.attention_backward(q, q, q, q, m, q, False, 0.1)          # HEAD_DIM 256
 
 
 def test_attention_rejects_unsupported():

@@ -1,4 +1,4 @@
-// Fused attention backward for sm_100a, HEAD_DIM 128, N_CTX a multiple of 128: dQ, dK, dV from Q, K, V, O, dO and the
+// Fused attention backward for sm_100a, HEAD_DIM 64 or 128, any N_CTX: dQ, dK, dV from Q, K, V, O, dO and the
 // row statistics M = m + log2(l) that the forward saves for exactly this purpose
 // (examples/fused-attn/06-fused-attention.py:238,269: `ctx.save_for_backward(q, k, v, o, M)`).  The reference stops
 // there (it has no backward kernel); this file completes the pair with the algorithm of the Triton tutorial the
@@ -101,11 +101,16 @@ __device__ __forceinline__ uint64_t koff_cols(int kk) {
 }
 __device__ __forceinline__ uint64_t koff_rows(int kk) { return static_cast<uint64_t>((kk * 2048) >> 4); }
 
-// One 128 x D tile: D / 64 TMA boxes.
-template <int D>
-__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row) {
+// One 128 x D tile: D / 64 TMA boxes; rows [row, row + 128) of batch*head hz.  RAGGED (N_CTX not a multiple of 128): the
+// tensor maps are three-dimensional (column, row in the head, head), so rows past the end of a head read as zero and
+// are not written, instead of spilling into the next head.
+template <int D, bool RAGGED>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int hz, int row, int n_ctx) {
 #pragma unroll
-  for (int bx = 0; bx < D / 64; ++bx) tma_load_2d(dst + bx * AT_BOX_BYTES, m, bar, bx * 64, row);
+  for (int bx = 0; bx < D / 64; ++bx) {
+    if (RAGGED) tma_load_3d(dst + bx * AT_BOX_BYTES, m, bar, bx * 64, row, hz);
+    else tma_load_2d(dst + bx * AT_BOX_BYTES, m, bar, bx * 64, hz * n_ctx + row);
+  }
 }
 
 // Tensor-memory column (relative to a 128-column fp32 tile) of the bf16 operand's k-step kk (16 values = 8 columns):
@@ -220,10 +225,11 @@ __device__ __forceinline__ void score_phase2(uint32_t t_dp, uint32_t t_dst, cons
 
 // Common epilogue of a score warp: one or two accumulators -> staging in the resident tiles -> TMA stores of the
 // warp's 32 rows x 64 columns; then the resident tiles and the accumulators are handed back.
+template <bool RAGGED>
 __device__ __forceinline__ void epilogue_store(uint32_t t_acc0, float scale0, uint8_t* stage0, const CUtensorMap* out0,
                                                bool two, uint32_t t_acc1, float scale1, uint8_t* stage1,
-                                               const CUtensorMap* out1, int r, int q, int half, int y, uint32_t lane,
-                                               uint64_t* acc_empty, uint64_t* res_empty, bool active) {
+                                               const CUtensorMap* out1, int r, int q, int half, int hz, int y, int n_ctx,
+                                               uint32_t lane, uint64_t* acc_empty, uint64_t* res_empty, bool active) {
   // HEAD_DIM 128: each half stores its 64-column box; HEAD_DIM 64: the one box is stored by the first half alone
   if (active) {
     store_acc(t_acc0, scale0, stage0, r, half);
@@ -235,8 +241,16 @@ __device__ __forceinline__ void epilogue_store(uint32_t t_acc0, float scale0, ui
   if (lane == 0) {
     mbar_arrive(acc_empty);
     if (active) {
-      tma_store_2d(out0, stage0 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
-      if (two) tma_store_2d(out1, stage1 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y);
+      // RAGGED: rows past the end of the head are clipped by the 3-D map (a warp whose 32 rows all lie past it stores nothing)
+      if (RAGGED) {
+        if (y < n_ctx) {
+          tma_store_3d(out0, stage0 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y, hz);
+          if (two) tma_store_3d(out1, stage1 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, y, hz);
+        }
+      } else {
+        tma_store_2d(out0, stage0 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, hz * n_ctx + y);
+        if (two) tma_store_2d(out1, stage1 + half * AT_BOX_BYTES + q * 32 * 128, half * 64, hz * n_ctx + y);
+      }
       tma_store_commit();
       tma_store_wait_read<0>();
     }
@@ -257,7 +271,7 @@ constexpr int kv_bar_off(int D) { return kv_vec_off(D) + KV_NSTAGE * 1024; }
 constexpr int kv_smem_total(int D) { return kv_bar_off(D) + KV_NBAR * 8 + 16 + 1024; }
 static_assert(kv_smem_total(128) <= 232448, "attention backward (dK/dV) shared memory budget exceeded");
 
-template <int BW_D>
+template <int BW_D, bool RAGGED>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -300,7 +314,7 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
     mbar_init(res_full, 1);
     mbar_init(res_empty, BW_SCORE_WARPS);
     for (int s = 0; s < KV_NSTAGE; ++s) {
-      mbar_init(&q_full[s], 1);
+      mbar_init(&q_full[s], RAGGED ? 2 : 1);   // RAGGED: the producer warp copies the M / delta vectors itself
       mbar_init(&q_empty[s], 1);
       mbar_init(&do_full[s], 1);
       mbar_init(&do_empty[s], 1);
@@ -342,8 +356,8 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       if (!ok) break;
       if (lane == 0) {
         mbar_expect_tx(res_full, 2 * BW_TILE_BYTES);
-        load_tile<BW_D>(smem_k, &tmap_k, res_full, row_base + n * AT_BN);
-        load_tile<BW_D>(smem_v, &tmap_v, res_full, row_base + n * AT_BN);
+        load_tile<BW_D, RAGGED>(smem_k, &tmap_k, res_full, hz, n * AT_BN, p.N_CTX);
+        load_tile<BW_D, RAGGED>(smem_v, &tmap_v, res_full, hz, n * AT_BN, p.N_CTX);
       }
       __syncwarp();
       for (int m = p.causal ? n : 0; ok && m < p.num_blk; ++m, ++g) {
@@ -352,17 +366,32 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
         ok = mbar_wait(&q_empty[st], ph ^ 1u, ctx, 81);
         if (!ok) break;
         if (lane == 0) {
-          mbar_expect_tx(&q_full[st], BW_TILE_BYTES + 1024);
-          load_tile<BW_D>(smem_q + st * BW_TILE_BYTES, &tmap_q, &q_full[st], row);
-          bulk_load_1d(smem_vec + st * 256, p.lse2 + row, 512, &q_full[st]);
-          bulk_load_1d(smem_vec + st * 256 + 128, p.delta + row, 512, &q_full[st]);
+          mbar_expect_tx(&q_full[st], BW_TILE_BYTES + (RAGGED ? 0 : 1024));
+          load_tile<BW_D, RAGGED>(smem_q + st * BW_TILE_BYTES, &tmap_q, &q_full[st], hz, m * AT_BM, p.N_CTX);
+          if (!RAGGED) {
+            bulk_load_1d(smem_vec + st * 256, p.lse2 + row, 512, &q_full[st]);
+            bulk_load_1d(smem_vec + st * 256 + 128, p.delta + row, 512, &q_full[st]);
+          }
+        }
+        if (RAGGED) {
+          // the block's M and delta values, zero past the end of the head (a bulk copy would run into the next head, or
+          // off the buffer): four of each per lane, then a second arrival on the stage's barrier
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int idx = static_cast<int>(lane) * 4 + e, qi = m * AT_BM + idx;
+            const bool in = qi < p.N_CTX;
+            smem_vec[st * 256 + idx] = in ? __ldg(p.lse2 + row_base + qi) : 0.f;
+            smem_vec[st * 256 + 128 + idx] = in ? __ldg(p.delta + row_base + qi) : 0.f;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&q_full[st]);
         }
         __syncwarp();
         ok = mbar_wait(&do_empty[st], ph ^ 1u, ctx, 82);
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&do_full[st], BW_TILE_BYTES);
-          load_tile<BW_D>(smem_do + st * BW_TILE_BYTES, &tmap_do, &do_full[st], row);
+          load_tile<BW_D, RAGGED>(smem_do + st * BW_TILE_BYTES, &tmap_do, &do_full[st], hz, m * AT_BM, p.N_CTX);
         }
         __syncwarp();
       }
@@ -496,9 +525,9 @@ attn_bwd_dkdv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const _
       ok = mbar_wait(acc_full, items & 1u, ctx, 92);
       if (!ok) break;
       tc_fence_after();
-      epilogue_store(tmem_base + lane_field + C_DV, 1.0f, smem_k, &tmap_dv, true, tmem_base + lane_field + C_DK, p.sm_scale,
-                     smem_v, &tmap_dk, r, q, half, hz * p.N_CTX + n * AT_BN + q * 32, lane, acc_empty, res_empty,
-                     BW_D == 128 || half == 0);
+      epilogue_store<RAGGED>(tmem_base + lane_field + C_DV, 1.0f, smem_k, &tmap_dv, true, tmem_base + lane_field + C_DK,
+                             p.sm_scale, smem_v, &tmap_dk, r, q, half, hz, n * AT_BN + q * 32, p.N_CTX, lane, acc_empty,
+                             res_empty, BW_D == 128 || half == 0);
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
@@ -525,7 +554,7 @@ constexpr int dq_bar_off(int D) { return (2 + DQ_NK + DQ_NV) * bw_tile_bytes(D);
 constexpr int dq_smem_total(int D) { return dq_bar_off(D) + DQ_NBAR * 8 + 16 + 1024; }
 static_assert(dq_smem_total(128) <= 232448, "attention backward (dQ) shared memory budget exceeded");
 
-template <int BW_D>
+template <int BW_D, bool RAGGED>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -610,13 +639,12 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++items) {
       int hz, m;
       item_block(item, hz, m);
-      const int row_base = hz * p.N_CTX;
       ok = mbar_wait(res_empty, (items & 1u) ^ 1u, ctx, 100);
       if (!ok) break;
       if (lane == 0) {
         mbar_expect_tx(res_full, 2 * BW_TILE_BYTES);
-        load_tile<BW_D>(smem_q, &tmap_q, res_full, row_base + m * AT_BM);
-        load_tile<BW_D>(smem_do, &tmap_do, res_full, row_base + m * AT_BM);
+        load_tile<BW_D, RAGGED>(smem_q, &tmap_q, res_full, hz, m * AT_BM, p.N_CTX);
+        load_tile<BW_D, RAGGED>(smem_do, &tmap_do, res_full, hz, m * AT_BM, p.N_CTX);
       }
       __syncwarp();
       const int n_end = p.causal ? m + 1 : p.num_blk;
@@ -626,14 +654,14 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&k_full[ks], BW_TILE_BYTES);
-          load_tile<BW_D>(smem_k + ks * BW_TILE_BYTES, &tmap_k, &k_full[ks], row_base + n * AT_BN);
+          load_tile<BW_D, RAGGED>(smem_k + ks * BW_TILE_BYTES, &tmap_k, &k_full[ks], hz, n * AT_BN, p.N_CTX);
         }
         __syncwarp();
         ok = mbar_wait(&v_empty[vs], vph ^ 1u, ctx, 102);
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&v_full[vs], BW_TILE_BYTES);
-          load_tile<BW_D>(smem_v + vs * BW_TILE_BYTES, &tmap_v, &v_full[vs], row_base + n * AT_BN);
+          load_tile<BW_D, RAGGED>(smem_v + vs * BW_TILE_BYTES, &tmap_v, &v_full[vs], hz, n * AT_BN, p.N_CTX);
         }
         __syncwarp();
       }
@@ -728,7 +756,8 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       int hz, m;
       item_block(item, hz, m);
       const int64_t my_row = static_cast<int64_t>(hz) * p.N_CTX + m * AT_BM + r;
-      const float m_i = __ldg(p.lse2 + my_row), d_i = __ldg(p.delta + my_row);
+      const bool row_in = !RAGGED || m * AT_BM + r < p.N_CTX;     // rows past the end of the head: computed, never stored
+      const float m_i = row_in ? __ldg(p.lse2 + my_row) : 0.f, d_i = row_in ? __ldg(p.delta + my_row) : 0.f;
       const int n_end = p.causal ? m + 1 : p.num_blk;
       for (int n = 0; ok && n < n_end; ++n, ++g) {
         const uint32_t t_s = tmem_base + lane_field + C_S + (g & 1u) * 128 + half * 64;
@@ -753,8 +782,8 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
       ok = mbar_wait(acc_full, items & 1u, ctx, 110);
       if (!ok) break;
       tc_fence_after();
-      epilogue_store(tmem_base + lane_field + C_DQ, p.sm_scale, smem_q, &tmap_dq, false, 0, 0.f, nullptr, nullptr, r, q, half,
-                     hz * p.N_CTX + m * AT_BM + q * 32, lane, acc_empty, res_empty, BW_D == 128 || half == 0);
+      epilogue_store<RAGGED>(tmem_base + lane_field + C_DQ, p.sm_scale, smem_q, &tmap_dq, false, 0, 0.f, nullptr, nullptr, r, q,
+                             half, hz, m * AT_BM + q * 32, p.N_CTX, lane, acc_empty, res_empty, BW_D == 128 || half == 0);
     }
     if (lane == 0) tma_store_wait_all<0>();
     __syncwarp();
@@ -773,12 +802,12 @@ attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
 // ---------------------------------------------------------------------------------------------------------------
 // Host
 // ---------------------------------------------------------------------------------------------------------------
-int attn_bwd_supported(int D, int N_CTX) { return ((D == 64 || D == 128) && N_CTX >= AT_BM && N_CTX % AT_BM == 0) ? 1 : 0; }
+int attn_bwd_supported(int D, int N_CTX) { return ((D == 64 || D == 128) && N_CTX >= 1) ? 1 : 0; }
 
 int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   if (a.Z <= 0 || a.H <= 0 || a.N_CTX <= 0) return set_error(B200K_ERR_INVALID_ARG, "attention backward: Z, H, N_CTX must be positive");
   if (!attn_bwd_supported(a.D, a.N_CTX))
-    return set_error(B200K_ERR_UNSUPPORTED, "attention backward: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 64 or 128, N_CTX a multiple of 128)", a.D, a.N_CTX);
+    return set_error(B200K_ERR_UNSUPPORTED, "attention backward: HEAD_DIM %d / N_CTX %d not supported (HEAD_DIM 64 or 128)", a.D, a.N_CTX);
   const void* ptrs[] = {a.q, a.k, a.v, a.o, a.d_o, a.lse2, a.dq, a.dk, a.dv, a.delta};
   for (const void* ptr : ptrs) {
     if (ptr == nullptr) return set_error(B200K_ERR_INVALID_ARG, "attention backward: null pointer");
@@ -794,18 +823,24 @@ int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   const uint64_t rows = static_cast<uint64_t>(zh) * a.N_CTX;
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   int rc;
-  if ((rc = make_tmap_bf16_2d(&tq, a.q, a.D, rows, a.D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tk, a.k, a.D, rows, a.D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tv, a.v, a.D, rows, a.D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdo, a.d_o, a.D, rows, a.D, 64, AT_BM)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdq, a.dq, a.D, rows, a.D, 64, 32)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdk, a.dk, a.D, rows, a.D, 64, 32)) != 0) return rc;
-  if ((rc = make_tmap_bf16_2d(&tdv, a.dv, a.D, rows, a.D, 64, 32)) != 0) return rc;
+  // N_CTX a multiple of 128: one 2-D map over all rows; otherwise per-head 3-D maps (column, row in the head, head)
+  const bool ragged = a.N_CTX % AT_BM != 0;
+  auto make_map = [&](CUtensorMap* m, const void* base, uint32_t box_rows) {
+    return ragged ? make_tmap_bf16_3d(m, base, a.D, a.N_CTX, zh, 64, box_rows)
+                  : make_tmap_bf16_2d(m, base, a.D, rows, a.D, 64, box_rows);
+  };
+  if ((rc = make_map(&tq, a.q, AT_BM)) != 0) return rc;
+  if ((rc = make_map(&tk, a.k, AT_BM)) != 0) return rc;
+  if ((rc = make_map(&tv, a.v, AT_BM)) != 0) return rc;
+  if ((rc = make_map(&tdo, a.d_o, AT_BM)) != 0) return rc;
+  if ((rc = make_map(&tdq, a.dq, 32)) != 0) return rc;
+  if ((rc = make_map(&tdk, a.dk, 32)) != 0) return rc;
+  if ((rc = make_map(&tdv, a.dv, 32)) != 0) return rc;
 
   BwdParams p;
   p.ZH = static_cast<int>(zh);
   p.N_CTX = a.N_CTX;
-  p.num_blk = a.N_CTX / AT_BM;
+  p.num_blk = (a.N_CTX + AT_BM - 1) / AT_BM;
   p.num_items = p.ZH * p.num_blk;
   p.causal = a.causal ? 1 : 0;
   p.sm_scale = a.sm_scale;
@@ -823,21 +858,26 @@ int attn_bwd_bf16(const AttnBwdArgs& a, cudaStream_t stream) {
   B200K_CHECK_LAUNCH("attn_bwd_delta_kernel");
 
   const int grid = p.num_items < dev->sm_count ? p.num_items : dev->sm_count;
-#define B200K_BWD_LAUNCH(DD)                                                                                                  \
+#define B200K_BWD_LAUNCH(DD, RR)                                                                                              \
   do {                                                                                                                       \
-    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_tcgen05_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dkdv_tcgen05_kernel<DD, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                                           kv_smem_total(DD)));                                                               \
-    attn_bwd_dkdv_tcgen05_kernel<DD><<<grid, BW_THREADS, kv_smem_total(DD), stream>>>(tq, tk, tv, tdo, tdk, tdv, p);         \
+    attn_bwd_dkdv_tcgen05_kernel<DD, RR><<<grid, BW_THREADS, kv_smem_total(DD), stream>>>(tq, tk, tv, tdo, tdk, tdv, p);     \
     count_launch();                                                                                                          \
     B200K_CHECK_LAUNCH("attn_bwd_dkdv_tcgen05_kernel");                                                                      \
-    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dq_tcgen05_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+    B200K_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_dq_tcgen05_kernel<DD, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                           dq_smem_total(DD)));                                                               \
-    attn_bwd_dq_tcgen05_kernel<DD><<<grid, BW_THREADS, dq_smem_total(DD), stream>>>(tq, tk, tv, tdo, tdq, p);                \
+    attn_bwd_dq_tcgen05_kernel<DD, RR><<<grid, BW_THREADS, dq_smem_total(DD), stream>>>(tq, tk, tv, tdo, tdq, p);            \
     count_launch();                                                                                                          \
     B200K_CHECK_LAUNCH("attn_bwd_dq_tcgen05_kernel");                                                                        \
   } while (0)
-  if (a.D == 64) B200K_BWD_LAUNCH(64);
-  else B200K_BWD_LAUNCH(128);
+  if (a.D == 64) {
+    if (ragged) B200K_BWD_LAUNCH(64, true);
+    else B200K_BWD_LAUNCH(64, false);
+  } else {
+    if (ragged) B200K_BWD_LAUNCH(128, true);
+    else B200K_BWD_LAUNCH(128, false);
+  }
 #undef B200K_BWD_LAUNCH
   return B200K_OK;
 }

@@ -474,7 +474,7 @@ def attention_backward(q, k, v, o, M, d_o, causal, sm_scale):
         raise ValueError("attention_backward: M must be [Z, H, N_CTX]")
     if not lib.b200k_attn_bwd_supported(D, N_CTX):
         raise NotImplementedError(f"attention backward: no sm_100a kernel for HEAD_DIM={D}, N_CTX={N_CTX} "
-                                  "(HEAD_DIM 64 or 128, N_CTX a multiple of 128)")
+                                  "(HEAD_DIM 64 or 128)")
     qd, kd, vd, od, dod, Md = (_to_device(t).contiguous() for t in (q, k, v, o, d_o, M))
     dq, dk, dv = torch.empty_like(qd), torch.empty_like(qd), torch.empty_like(qd)
     delta = torch.empty((Z, H, N_CTX), device=qd.device, dtype=torch.float32)
