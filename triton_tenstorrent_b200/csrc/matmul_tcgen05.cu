@@ -41,6 +41,7 @@ constexpr int MM_C_STAGING_BYTES = MM_EPI_WARPS * 2 * MM_C_BUF_BYTES;  // 32 KB
 struct MatmulParams {
   int M, N, K;
   int num_pid_m, num_pid_n, group_m;
+  int serpentine;   // odd groups of tile rows walk the tile columns backwards
   int num_tiles, num_kb;
   // CTA-pair kernel: work items [0, full_work) are whole 256 x 256 tiles; items beyond are the tiles of the last,
   // less than half full wave cut in two 256 x 128 halves, so that twice as many pairs share it (num_work items in all)
@@ -87,6 +88,8 @@ __device__ __forceinline__ void tile_coords(const MatmulParams& p, int tile, int
   const int in_group = tile - group_id * num_pid_in_group;
   pid_m = first_pid_m + (in_group % group_size_m);
   pid_n = in_group / group_size_m;
+  // the next group of rows starts with the B columns the previous group finished with (still in L2)
+  if (p.serpentine && (group_id & 1)) pid_n = p.num_pid_n - 1 - pid_n;
 }
 
 // 16-bit element <-> fp32 in the operand type of the launch (bf16 or fp16; warp-uniform flag)
@@ -669,6 +672,8 @@ static int launch_matmul(const MatmulArgs& a, const DeviceInfo* dev, cudaStream_
   p.num_pid_n = (a.N + BN - 1) / BN;
   p.group_m = 16;  // 16 tile rows of 128 = 2048 rows of A (33.5 MB at K = 8192) stay hot in L2
   if (const char* g = getenv("B200K_MATMUL_GROUP_M")) { int v = atoi(g); if (v > 0) p.group_m = v; }
+  p.serpentine = 1;
+  if (const char* g = getenv("B200K_MATMUL_SERPENTINE")) p.serpentine = atoi(g) != 0;
   p.num_tiles = p.num_pid_m * p.num_pid_n;
   p.num_kb = (a.K + MM_BK - 1) / MM_BK;
   p.bias_row = (a.bias_kind == B200K_BIAS_ROW_F32) ? static_cast<const float*>(a.bias) : nullptr;
@@ -742,6 +747,8 @@ static int launch_matmul_2cta(const MatmulArgs& a, const DeviceInfo* dev, cudaSt
   p.num_pid_n = (a.N + MM2_BN - 1) / MM2_BN;
   p.group_m = 8;  // 8 tile rows of 256 = 2048 rows of A stay hot in L2 while the tile columns stream
   if (const char* g = getenv("B200K_MATMUL_GROUP_M")) { int v = atoi(g); if (v > 0) p.group_m = v; }
+  p.serpentine = 1;
+  if (const char* g = getenv("B200K_MATMUL_SERPENTINE")) p.serpentine = atoi(g) != 0;
   p.num_tiles = p.num_pid_m * p.num_pid_n;
   p.num_kb = (a.K + MM_BK - 1) / MM_BK;
   p.bias_row = (a.bias_kind == B200K_BIAS_ROW_F32) ? static_cast<const float*>(a.bias) : nullptr;
