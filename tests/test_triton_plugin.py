@@ -1,8 +1,8 @@
 """The library registered with Triton as a backend + driver (triton_tenstorrent_b200/triton_plugin.py), the way
 the reference plugs itself in (backend/compiler.py, backend/driver.py:445-535).
 
-CPU part: the reference's example files are loaded UNMODIFIED from a checkout of the reference (REFERENCE_ROOT, or
-/root/reference when it exists), their `@triton.jit` kernels go through Triton's own front end and this backend's
+CPU part: the reference's example files are loaded UNMODIFIED from a checkout of the reference (the directory named
+by REFERENCE_ROOT, or the default checkout location when it exists), their `@triton.jit` kernels go through Triton's own front end and this backend's
 stages, and a recording launcher checks what would reach b200k_launch.  Skipped where no checkout is available.
 GPU part: the same path with real launches; a kernel written here stands in where no checkout is available.
 """
