@@ -583,6 +583,12 @@ def secondary_workloads(torch, ops, gi, peaks, sampler_index):
         if Dh == 64:
             out["attention_fwd_full_d64"]["ex2_roofline_TFLOP/s"] = xu_tflops_d64
             out["attention_fwd_full_d64"]["frac_of_ex2_roofline"] = t / xu_tflops_d64
+            # the backward at HEAD_DIM 64: the same 2 x 4.29e9 exponentials (both kernels recompute P) for half the flop
+            o, m = ops.attention_with_lse(q, k, v, False, Dh ** -0.5)
+            d_o = torch.randn_like(q)
+            ms = quick_ms(lambda: ops.attention_backward(q, k, v, o, m, d_o, False, Dh ** -0.5), torch, rep=10)
+            out["attention_bwd_full_d64"] = {"ms": ms, "TFLOP/s": 10.0 * Z * Hh * S * S * Dh / ms / 1e9, "launches": 3}
+            del o, m, d_o
         del q, k, v
 
     # matmul 4096^3 and 16384^3 (the other sizes of the workload definition)
