@@ -809,6 +809,43 @@ def test_attention_backward_repeats_bit_for_bit(S, D, causal):
     assert ops.device_status() == 0
 
 
+def _random_attention_shapes(n, seed, dims):
+    rng = np.random.RandomState(seed)
+    shapes = []
+    for _ in range(n):
+        shapes.append((int(rng.randint(1, 3)), int(rng.randint(1, 5)), int(rng.randint(1, 700)), int(rng.choice(dims)),
+                       bool(rng.randint(0, 2))))
+    return shapes
+
+
+@pytest.mark.parametrize("Z,H,S,D,causal", _random_attention_shapes(24, 71, (64, 128)))
+def test_attention_forward_and_backward_random_shapes(Z, H, S, D, causal):
+    # seeded random (Z, H, N_CTX, HEAD_DIM, causal): lengths that end anywhere inside a block, single-block heads, more
+    # and fewer items than SMs; forward and backward against the CPU oracle
+    scale = D ** -0.5
+    q, k, v = gi.attn_inputs(Z, H, S, D, seed=72)
+    d_o = _d_o(Z, H, S, D, seed=73)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    o, m = ops.attention_with_lse(qd, kd, vd, causal, scale)
+    blk = 1
+    for b in (128, 64, 32, 25, 16, 9, 8, 4, 3, 2):       # an oracle block size that divides N_CTX (the reference walks
+        if S % b == 0 and b <= D:                        # whole blocks: it has no keys past N_CTX only then)
+            blk = b
+            break
+    ro, rm = oracle.attention(q, k, v, causal, scale, BLOCK_M=blk, BLOCK_N=blk)
+    assert float((o.cpu().float() - ro.float()).abs().max()) <= ATTN_MAX_ABS
+    assert float((m.cpu() - rm).abs().max()) <= 1e-3
+    grads = ops.attention_backward(qd, kd, vd, o, m, d_o.cuda(), causal, scale)
+    ref = oracle.attention_backward(q, k, v, o.cpu(), d_o, m.cpu(), causal, scale)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    for name, got, want in zip(("dq", "dk", "dv"), grads, ref):
+        assert bool(torch.isfinite(got.float()).all()), name
+        diff = (got.cpu().float() - want.float())
+        assert float(diff.norm()) <= 1e-2 * float(want.float().norm()) + 1e-3, name
+        assert float(diff.abs().max()) <= 3e-2, name
+
+
 def test_attention_backward_single_key():
     # N_CTX = 1: the softmax of one score is 1 whatever q and k are, so dv = dO and dq = dk = 0 (up to the rounding
     # difference between the MMA's dO.V and the delta kernel's O.dO)
