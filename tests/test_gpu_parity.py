@@ -238,6 +238,42 @@ def test_matmul_strided_operands_and_canaries():
     assert oracle.rel_frobenius(host[:M, :N].float(), ref.float()) <= MATMUL_REL_FRO
 
 
+def _random_matmul_shapes(n, seed):
+    rng = np.random.RandomState(seed)
+    return [(int(rng.randint(1, 2000)), 8 * int(rng.randint(1, 260)), 8 * int(rng.randint(1, 130)), int(rng.randint(0, 4)))
+            for _ in range(n)]
+
+
+@pytest.mark.parametrize("M,N,K,mode", _random_matmul_shapes(24, 81))
+def test_matmul_random_shapes(M, N, K, mode):
+    # seeded random sizes (any M; N and K multiples of 8, the 16-byte row rule of TMA): single-CTA and CTA-pair kernels,
+    # whole / half / missing last waves, with each epilogue; C sits between canaries
+    a, b, bias_full = gi.fused_inputs(M, N, K, seed=82)
+    ad, bd = a.cuda(), b.cuda()
+    pad = 1024
+    buf = torch.full((M * N + 2 * pad,), 7.5, dtype=torch.bfloat16, device="cuda")
+    c = buf[pad:pad + M * N].view(M, N)
+    if mode == 0:
+        got, ref = ops._matmul_call(ad, bd, c=c), oracle.golden_matmul(a, b)
+    elif mode == 1:
+        got, ref = ops.matmul(ad, bd, activation="leaky_relu"), oracle.golden_matmul(a, b, mode=0, activation="leaky_relu")
+    elif mode == 2:
+        bias_row = gi.row_bias(N)
+        got, ref = (ops.matmul_fused(ad, bd, bias_row.cuda(), activation="relu"),
+                    oracle.golden_matmul(a, b, bias=bias_row, mode=3, activation="relu"))
+    else:
+        got, ref = ops.matmul_tma_fused(ad, bd, bias_full.cuda(), True), oracle.golden_matmul(a, b, bias=bias_full, mode=2)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    got = got.cpu()
+    assert tuple(got.shape) == (M, N)
+    denom = float(ref.float().norm())
+    assert float((got.float() - ref.float()).norm()) <= MATMUL_REL_FRO * denom + 1e-3
+    if mode == 0:
+        assert not torch.any(got == 7.5), "an element of C was left unwritten"
+        assert bool((buf[:pad] == 7.5).all()) and bool((buf[pad + M * N:] == 7.5).all())
+
+
 def test_matmul_activation_and_bias_epilogues():
     M, N, K = 384, 320, 256
     a, b, bias_full = gi.fused_inputs(M, N, K, seed=6)
