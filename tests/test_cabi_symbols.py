@@ -66,6 +66,15 @@ def test_argument_errors_before_any_device_work():
     assert lib.b200k_attn_bwd_supported(128, 4096) == 1 and lib.b200k_attn_bwd_supported(64, 256) == 1
     assert lib.b200k_attn_bwd_supported(32, 256) == 0 and lib.b200k_attn_bwd_supported(128, 192) == 1 and lib.b200k_attn_bwd_supported(64, 0) == 0
     assert lib.b200k_attn_bwd_bf16(16, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 256, 256, 0, 0.1, None) == _lib.ERR_UNSUPPORTED
+    # argument checks of the backward come before any device work
+    assert lib.b200k_attn_bwd_bf16(16, 16, 16, 16, 16, 16, 16, 16, 16, 16, 0, 1, 256, 128, 0, 0.1, None) == _lib.ERR_INVALID_ARG
+    assert lib.b200k_attn_bwd_bf16(16, 16, 16, 16, 16, 16, 16, 16, None, 16, 1, 1, 256, 128, 0, 0.1, None) == _lib.ERR_INVALID_ARG
+    assert "null" in _lib.last_error()
+    assert lib.b200k_attn_bwd_bf16(16, 16, 16, 16, 16, 16, 16, 24, 16, 16, 1, 1, 256, 128, 0, 0.1, None) == _lib.ERR_INVALID_ARG
+    assert "16-byte" in _lib.last_error()
+    assert lib.b200k_attn_bwd_bf16(16, 16, 16, 16, 16, 16, 16, 16, 16, 16, 1, 1, 256, 128, 0, 0.0, None) == _lib.ERR_INVALID_ARG
+    assert lib.b200k_attn_bwd_bf16(16, 16, 16, 16, 16, 16, 16, 16, 16, 16, 2 ** 20, 2 ** 11, 2 ** 10, 128, 0, 0.1, None) == _lib.ERR_INVALID_ARG
+    assert "2^31" in _lib.last_error()
     assert lib.b200k_launch(b"no_such_kernel", 1, 1, 1, None, None, 0) == _lib.ERR_UNSUPPORTED
     assert lib.b200k_launch(b"add_kernel", 0, 1, 1, None, None, 0) == _lib.ERR_INVALID_ARG
     with pytest.raises(_lib.B200KError):
