@@ -535,7 +535,11 @@ def secondary_workloads(torch, ops, gi, peaks, sampler_index):
     out["sin_n2^26"] = {"ms": ms, "GB/s": 8 * n / ms / 1e6, "frac_of_hbm_peak": 8 * n / ms / 1e6 / hbm,
                         "l2": "inputs larger than L2, back-to-back launches", "ms_flushed_single": msf,
                         "GB/s_flushed_single": 8 * n / msf / 1e6}
-    del xb, yb, xs
+    # the Gluon intro's memcpy (python/tutorials/gluon/01-intro.py reports 666 GB/s on GB200 for its one-element-per-step kernel)
+    cp_out = torch.empty_like(xs)
+    ms = quick_ms(lambda: ops.memcpy(xs, cp_out), torch, rep=30)
+    out["memcpy_n2^26"] = {"ms": ms, "GB/s": 8 * n / ms / 1e6, "frac_of_hbm_peak": 8 * n / ms / 1e6 / hbm}
+    del xb, yb, xs, cp_out
 
     # fused-epilogue matmul: ReLU(A.B + bias[N]), M=16384, N=K=4096
     Mf, Nf, Kf = 16384, 4096, 4096

@@ -66,6 +66,13 @@ int b200k_add_bf16(const void* x, const void* y, void* out, int64_t n, int block
 int b200k_sin_f32(const float* x, float* out, int64_t n, int block, void* stream);
 
 /*
+ * out[i] = x[i] for i < n, fp32 words copied bit for bit (NaN payloads included).  x and out must not overlap.
+ * Replaces: memcpy_kernel, python/tutorials/gluon/01-intro.py:84-93 (launch :96-99; XBLOCK = block) and
+ * copy_scalar_kernel of the same file (:60-63, n = 1).
+ */
+int b200k_copy_f32(const float* x, float* out, int64_t n, int block, void* stream);
+
+/*
  * out[i] = x[i] * y[i] + z[i] (one fused multiply-add is NOT used: product and sum are
  * rounded separately like the reference's two Triton ops).
  * Replaces: python/tutorials/01-vector-mul-add.py (x*y+z variant of add_kernel).
@@ -223,9 +230,9 @@ int b200k_attn_bwd_supported(int D, int N_CTX);
  * Generic launch mirroring the argument list the reference launcher builds
  * (backend/driver.py:98-170 TTLauncher.__call__: constexprs dropped, tensors as pointers,
  * TensorDescriptor flattened to base, shape.., strides.., padding flag, shape.., strides..).
- * kernel_name is one of: "add_kernel", "sin_kernel", "mul_add_kernel", "matmul_kernel_tma",
- * "matmul_kernel_fused", "_attn_fwd", optionally followed by ":KEY=VALUE,..." with the constexpr values
- * the reference bakes into the compiled kernel (BLOCK_SIZE, BLOCK_SIZE_M/N, STAGE, and F16=1 for the
+ * kernel_name is one of: "add_kernel", "sin_kernel", "mul_add_kernel", "memcpy_kernel", "copy_scalar_kernel",
+ * "matmul_kernel_tma", "matmul_kernel_fused", "matmul_kernel", "_attn_fwd", optionally followed by ":KEY=VALUE,..." with the constexpr values
+ * the reference bakes into the compiled kernel (BLOCK_SIZE, XBLOCK, BLOCK_SIZE_M/N, STAGE, and F16=1 for the
  * matmul kernels when the descriptors point at fp16 data).  The grid is validated against the problem size
  * implied by the arguments; it does not change the result.
  */

@@ -48,6 +48,7 @@ def load() -> ctypes.CDLL:
     lib.oracle_add_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int]
     lib.oracle_add_loop.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int]
     lib.oracle_sin_f32.argtypes = [c_void_p, c_void_p, c_int64, c_int, c_int]
+    lib.oracle_memcpy_f32.argtypes = [c_void_p, c_void_p, c_int64, c_int, c_int]
     lib.oracle_sin_f64_to_f32.argtypes = [c_void_p, c_void_p, c_int64]
     lib.oracle_mul_add_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int]
     lib.oracle_golden_matmul.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
@@ -58,7 +59,7 @@ def load() -> ctypes.CDLL:
                                          c_int, c_float, c_int, c_int]
     lib.oracle_attn_bwd_bf16.argtypes = [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_int, c_float]
     lib.oracle_attn_bwd_bf16.restype = None
-    for fn in ("oracle_block_range", "oracle_add_f32", "oracle_add_loop", "oracle_sin_f32", "oracle_sin_f64_to_f32", "oracle_mul_add_f32",
+    for fn in ("oracle_block_range", "oracle_add_f32", "oracle_add_loop", "oracle_sin_f32", "oracle_memcpy_f32", "oracle_sin_f64_to_f32", "oracle_mul_add_f32",
                "oracle_golden_matmul", "oracle_golden_matmul_naive", "oracle_matmul_kernel_tile32", "oracle_attn_fwd_bf16"):
         getattr(lib, fn).restype = None
     _lib = lib
@@ -111,6 +112,14 @@ def sin(x, block: int = 1024, workers: int = 0):
     x = _cpu(x, torch.float32)
     out = torch.empty_like(x)
     load().oracle_sin_f32(x.data_ptr(), out.data_ptr(), x.numel(), block, workers)
+    return out
+
+
+def memcpy(x, xblock: int = 2048, workers: int = 0):
+    """memcpy_kernel of python/tutorials/gluon/01-intro.py:84-93, block by block."""
+    x = _cpu(x, torch.float32)
+    out = torch.full_like(x, float("nan"))
+    load().oracle_memcpy_f32(x.data_ptr(), out.data_ptr(), x.numel(), xblock, workers)
     return out
 
 

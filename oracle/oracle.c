@@ -148,6 +148,25 @@ void oracle_sin_f32(const float* x, float* out, int64_t n, int block, int worker
   }
 }
 
+/* memcpy_kernel, python/tutorials/gluon/01-intro.py:84-93: program pid copies elements [pid*XBLOCK, min(.., xnumel))
+ * one at a time (gl.load / gl.store of a scalar); words are moved as integers so that no NaN payload can change. */
+void oracle_memcpy_f32(const float* in, float* out, int64_t xnumel, int xblock, int workers) {
+  const uint32_t* src = (const uint32_t*)in;
+  uint32_t* dst = (uint32_t*)out;
+  const int64_t nb = (xnumel + xblock - 1) / xblock;
+  if (workers <= 0) workers = oracle_max_threads();
+#pragma omp parallel for num_threads(workers) schedule(static, 1)
+  for (int w = 0; w < workers; ++w) {
+    int64_t bs, be;
+    oracle_block_range(nb, workers, w, &bs, &be);
+    for (int64_t pid = bs; pid < be; ++pid) {
+      const int64_t start = pid * xblock;
+      const int64_t end = start + xblock < xnumel ? start + xblock : xnumel;
+      for (int64_t i = start; i < end; ++i) dst[i] = src[i];
+    }
+  }
+}
+
 /* Correctly rounded reference for the ulp bound: sin in double, rounded once to fp32. */
 void oracle_sin_f64_to_f32(const float* x, float* out, int64_t n) {
 #pragma omp parallel for schedule(static)

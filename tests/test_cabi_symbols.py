@@ -77,5 +77,8 @@ def test_argument_errors_before_any_device_work():
     assert "2^31" in _lib.last_error()
     assert lib.b200k_launch(b"no_such_kernel", 1, 1, 1, None, None, 0) == _lib.ERR_UNSUPPORTED
     assert lib.b200k_launch(b"add_kernel", 0, 1, 1, None, None, 0) == _lib.ERR_INVALID_ARG
+    assert lib.b200k_launch(b"memcpy_kernel:XBLOCK=64", 1, 1, 1, None, None, 0) == _lib.ERR_INVALID_ARG   # no arguments
+    assert lib.b200k_copy_f32(None, None, 4, 64, None) == _lib.ERR_INVALID_ARG and "null" in _lib.last_error()
+    assert lib.b200k_copy_f32(None, None, 0, 64, None) == _lib.OK                                       # nothing to copy
     with pytest.raises(_lib.B200KError):
         _lib.check(lib.b200k_launch(b"add_kernel", 1, 1, 1, None, None, 0))  # wrong argument count

@@ -160,6 +160,47 @@ def test_sin_ragged_and_special_values():
     assert math.copysign(1.0, got[1].item()) == -1.0    # sin(-0) = -0
 
 
+# ------------------------------------------------------------------------------------------------ memcpy (Gluon intro)
+@pytest.mark.parametrize("n,xblock", [(1, 64), (40, 64), (500, 64), (98432, 1024), (2 ** 22 + 3, 2048)])
+def test_memcpy_bit_exact(n, xblock):
+    # memcpy_kernel / memcpy(), python/tutorials/gluon/01-intro.py:84-99 (its own tests: xnumel 40 and 500, XBLOCK 64, atol 0)
+    g = torch.Generator(device="cpu").manual_seed(n)
+    x = torch.randn(n, generator=g, dtype=torch.float32)
+    bits = x.view(torch.int32)
+    bits[::7] = torch.tensor(0x7FC12345, dtype=torch.int32)        # NaNs with a payload
+    bits[3::11] = torch.tensor(0x7F800001, dtype=torch.int32)      # a signalling NaN: must not be quieted
+    if n > 2:
+        x[1], x[2] = float("inf"), -0.0
+    ref = oracle.memcpy(x, xblock)
+    assert torch.equal(ref.view(torch.int32), x.view(torch.int32))
+    pad = 64
+    buf = torch.full((n + 2 * pad,), -7.0, device="cuda")
+    out = buf[pad:pad + n]
+    ops.memcpy(x.cuda(), out, xblock)
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu().view(torch.int32), ref.view(torch.int32))
+    assert bool((buf[:pad] == -7.0).all()) and bool((buf[pad + n:] == -7.0).all())
+    # unaligned source and destination (scalar path), through the kernel[grid] surface
+    if n > 8:
+        xs = x.cuda()
+        dst = torch.full((n,), -7.0, device="cuda")
+        kernels.memcpy_kernel[((n - 1 + xblock - 1) // xblock,)](xs[1:], dst[1:], n - 1, xblock, num_warps=1)
+        torch.cuda.synchronize()
+        assert torch.equal(dst[1:].cpu().view(torch.int32), x[1:].view(torch.int32)) and float(dst[0]) == -7.0
+
+
+def test_copy_scalar_and_full_size():
+    x = torch.tensor([42.0], device="cuda")                      # test_copy_scalar of the reference file
+    out = torch.empty_like(x)
+    kernels.copy_scalar_kernel[(1,)](x, out, num_warps=1)
+    assert float(out[0]) == 42.0
+    n = 2 ** 26
+    big = torch.rand(n, device="cuda")
+    got = ops.memcpy(big)
+    assert torch.equal(got, big)
+    assert ops.device_status() == 0
+
+
 # ------------------------------------------------------------------------------------------------ matmul
 @pytest.mark.parametrize("shape", gi.MATMUL_SHAPES)
 def test_matmul_golden(golden_dir, shape):

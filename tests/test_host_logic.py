@@ -36,7 +36,7 @@ def recording(monkeypatch):
     monkeypatch.setattr(driver.active, "launcher_cls", RecordingLauncher)
     monkeypatch.setattr(driver.active, "get_current_stream", lambda device_id=None: 0)
     for k in (kernels.add_kernel, kernels.add_kernel_loop, kernels.sin_kernel, kernels.matmul_kernel_tma, kernels.matmul_kernel_fused,
-              kernels.matmul_kernel, kernels._attn_fwd):
+              kernels.matmul_kernel, kernels._attn_fwd, kernels.memcpy_kernel, kernels.copy_scalar_kernel):
         monkeypatch.setattr(k, "launcher", None)
     return RecordingLauncher.calls
 
@@ -54,6 +54,22 @@ def test_add_kernel_launch_surface(recording):
     assert kinds == [_lib.ARG_PTR] * 3 + [_lib.ARG_I32]    # the constexpr BLOCK_SIZE is dropped
     assert call["flat"][3][1] == n
     assert [v for _, v in call["flat"][:3]] == [x.data_ptr(), y.data_ptr(), out.data_ptr()]
+
+
+def test_memcpy_kernel_launch_surface(recording):
+    # memcpy_kernel[grid](input, output, xnumel, XBLOCK, num_warps=1) and copy_scalar_kernel[(1,)](input, output, num_warps=1),
+    # python/tutorials/gluon/01-intro.py:96-99 and :60-63
+    n = 500
+    x, out = fake(torch.zeros(n)), fake(torch.zeros(n))
+    kernels.memcpy_kernel[((n + 63) // 64,)](x, out, n, 64, num_warps=1)
+    call = recording[0]
+    assert call["grid"] == (8, 1, 1) and call["function"] == "memcpy_kernel:XBLOCK=64"
+    assert [k for k, _ in call["flat"]] == [_lib.ARG_PTR, _lib.ARG_PTR, _lib.ARG_I32]      # the constexpr XBLOCK is dropped
+    assert [v for _, v in call["flat"]] == [x.data_ptr(), out.data_ptr(), n]
+    kernels.copy_scalar_kernel[(1,)](x, out, num_warps=1)
+    call = recording[1]
+    assert call["grid"] == (1, 1, 1) and call["function"] == "copy_scalar_kernel"
+    assert [k for k, _ in call["flat"]] == [_lib.ARG_PTR, _lib.ARG_PTR]
 
 
 def test_add_kernel_loop_launch_surface(recording):

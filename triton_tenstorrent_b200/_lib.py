@@ -69,6 +69,7 @@ SIGNATURES = {
     "b200k_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "b200k_add_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "b200k_sin_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "b200k_copy_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "b200k_mul_add_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "b200k_matmul_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                                   c_void_p, c_int, c_int64, c_int, c_int, c_void_p]),

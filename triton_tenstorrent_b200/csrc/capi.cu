@@ -312,6 +312,21 @@ static int generic_launch(const char* kernel_name, int gx, int gy, int gz, cudaS
   }
   ArgCursor c{args, nargs};
   if (name == "muladd_kernel") name = "mul_add_kernel";   // the spelling of python/tutorials/01-vector-mul-add.py:29
+  if (name == "memcpy_kernel" || name == "copy_scalar_kernel") {
+    // python/tutorials/gluon/01-intro.py: memcpy_kernel(in_ptr, out_ptr, xnumel, XBLOCK: constexpr) :84-93 and
+    // copy_scalar_kernel(in_ptr, out_ptr) :50-53 (one element, one program)
+    if (gy != 1 || gz != 1) return set_error(B200K_ERR_INVALID_ARG, "launch %s: 1-D grid expected", name.c_str());
+    void* src = c.ptr();
+    void* dst = c.ptr();
+    const int64_t n = name == "memcpy_kernel" ? c.integer() : 1;
+    if (c.fail || c.i != nargs) return set_error(B200K_ERR_INVALID_ARG, "launch %s: expected two pointers%s, got %d arguments", name.c_str(), name == "memcpy_kernel" ? " and xnumel" : "", nargs);
+    if (n < 0) return set_error(B200K_ERR_INVALID_ARG, "launch %s: negative xnumel", name.c_str());
+    const long block = spec_value(spec, "XBLOCK", 0);
+    if (block > 0 && static_cast<int64_t>(gx) * block < n)
+      return set_error(B200K_ERR_INVALID_ARG, "launch %s: grid %d x XBLOCK %ld does not cover xnumel=%lld", name.c_str(), gx, block, (long long)n);
+    if (n > 0 && (src == nullptr || dst == nullptr)) return set_error(B200K_ERR_INVALID_ARG, "launch %s: null pointer", name.c_str());
+    return copy_f32((const float*)src, (float*)dst, n, stream);
+  }
   if (name == "add_kernel" || name == "sin_kernel" || name == "mul_add_kernel") {
     if (gy != 1 || gz != 1) return set_error(B200K_ERR_INVALID_ARG, "launch %s: 1-D grid expected", name.c_str());
     const int nptr = name == "add_kernel" ? 3 : (name == "sin_kernel" ? 2 : 4);
@@ -463,6 +478,14 @@ int b200k_sin_f32(const float* x, float* out, int64_t n, int block, void* stream
   if (block <= 0) return set_error(B200K_ERR_INVALID_ARG, "sin: BLOCK_SIZE must be positive (got %d)", block);
   if (n > 0 && (x == nullptr || out == nullptr)) return set_error(B200K_ERR_INVALID_ARG, "sin: null pointer");
   return sin_f32(x, out, n, static_cast<cudaStream_t>(stream));
+}
+
+int b200k_copy_f32(const float* x, float* out, int64_t n, int block, void* stream) {
+  clear_error();
+  if (n < 0) return set_error(B200K_ERR_INVALID_ARG, "copy: n must be >= 0 (got %lld)", (long long)n);
+  if (block <= 0) return set_error(B200K_ERR_INVALID_ARG, "copy: XBLOCK must be positive (got %d)", block);
+  if (n > 0 && (x == nullptr || out == nullptr)) return set_error(B200K_ERR_INVALID_ARG, "copy: null pointer");
+  return copy_f32(x, out, n, static_cast<cudaStream_t>(stream));
 }
 
 int b200k_mul_add_f32(const float* x, const float* y, const float* z, float* out, int64_t n, int block, void* stream) {

@@ -16,7 +16,10 @@
 
 namespace b200k {
 
-enum class EwOp { Add, Sin, MulAdd };
+enum class EwOp { Add, Sin, MulAdd, Copy };
+
+template <EwOp OP>
+constexpr bool ew_unary() { return OP == EwOp::Sin || OP == EwOp::Copy; }
 
 template <EwOp OP>
 __device__ __forceinline__ float ew_apply(float x, float y, float z) {
@@ -24,6 +27,8 @@ __device__ __forceinline__ float ew_apply(float x, float y, float z) {
     return x + y;
   } else if constexpr (OP == EwOp::Sin) {
     return sinf(x);
+  } else if constexpr (OP == EwOp::Copy) {
+    return x;   // bits preserved: a float move never quiets a NaN payload
   } else {
     return __fadd_rn(__fmul_rn(x, y), z);  // keep the two roundings of the reference's x*y then +z
   }
@@ -62,7 +67,7 @@ template <EwOp OP>
 __global__ void __launch_bounds__(EW_THREADS) ew_vec4_kernel(const float4* __restrict__ x, const float4* __restrict__ y,
                                                              const float4* __restrict__ z, float4* __restrict__ out,
                                                              int64_t n4) {
-  constexpr bool HAS_Y = (OP != EwOp::Sin);
+  constexpr bool HAS_Y = !ew_unary<OP>();
   constexpr bool HAS_Z = (OP == EwOp::MulAdd);
   const int64_t tile = static_cast<int64_t>(EW_THREADS) * EW_UNROLL;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * tile;
@@ -93,7 +98,7 @@ __global__ void __launch_bounds__(EW_THREADS) ew_scalar_kernel(const float* __re
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
     const float xv = x[i];
-    const float yv = (OP != EwOp::Sin) ? y[i] : 0.f;
+    const float yv = !ew_unary<OP>() ? y[i] : 0.f;
     const float zv = (OP == EwOp::MulAdd) ? z[i] : 0.f;
     out[i] = ew_apply<OP>(xv, yv, zv);
   }
@@ -106,7 +111,7 @@ static int ew_launch(const float* x, const float* y, const float* z, float* out,
   if (n == 0) return B200K_OK;
   const DeviceInfo* dev = current_device_info();
   if (dev == nullptr) return B200K_ERR_NO_DEVICE;
-  const bool vec_ok = aligned16(x) && aligned16(out) && (OP == EwOp::Sin || aligned16(y)) &&
+  const bool vec_ok = aligned16(x) && aligned16(out) && (ew_unary<OP>() || aligned16(y)) &&
                       (OP != EwOp::MulAdd || aligned16(z));
   const int64_t n4 = vec_ok ? (n / 4) : 0;
   if (n4 > 0) {
@@ -210,6 +215,9 @@ int add_f32(const float* x, const float* y, float* out, int64_t n, cudaStream_t 
 }
 int sin_f32(const float* x, float* out, int64_t n, cudaStream_t s) {
   return ew_launch<EwOp::Sin>(x, nullptr, nullptr, out, n, s);
+}
+int copy_f32(const float* x, float* out, int64_t n, cudaStream_t s) {
+  return ew_launch<EwOp::Copy>(x, nullptr, nullptr, out, n, s);
 }
 int mul_add_f32(const float* x, const float* y, const float* z, float* out, int64_t n, cudaStream_t s) {
   return ew_launch<EwOp::MulAdd>(x, y, z, out, n, s);

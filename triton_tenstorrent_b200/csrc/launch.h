@@ -74,6 +74,7 @@ struct alignas(64) ExtraMaps {
 int add_f32(const float* x, const float* y, float* out, int64_t n, cudaStream_t s);
 int add_bf16(const uint16_t* x, const uint16_t* y, uint16_t* out, int64_t n, cudaStream_t s);
 int sin_f32(const float* x, float* out, int64_t n, cudaStream_t s);
+int copy_f32(const float* x, float* out, int64_t n, cudaStream_t s);
 int mul_add_f32(const float* x, const float* y, const float* z, float* out, int64_t n, cudaStream_t s);
 
 struct MatmulArgs {

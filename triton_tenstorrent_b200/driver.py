@@ -28,7 +28,7 @@ from .tensor_descriptor import TensorDescriptor
 GPUTarget = namedtuple("GPUTarget", ["backend", "arch", "warp_size"])
 
 # kernels this library implements (the reference's compiled-kernel names)
-KERNEL_NAMES = ("add_kernel", "sin_kernel", "mul_add_kernel", "muladd_kernel", "matmul_kernel_tma", "matmul_kernel_fused", "matmul_kernel",
+KERNEL_NAMES = ("add_kernel", "sin_kernel", "mul_add_kernel", "muladd_kernel", "memcpy_kernel", "copy_scalar_kernel", "matmul_kernel_tma", "matmul_kernel_fused", "matmul_kernel",
                 "_attn_fwd")
 
 

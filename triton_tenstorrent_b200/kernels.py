@@ -112,6 +112,13 @@ sin_kernel = Kernel(
     "sin_kernel", ["x_ptr", "output_ptr", "n_elements", "BLOCK_SIZE"],
     ["*fp32", "*fp32", "i32", "constexpr"], {}, spec_keys=("BLOCK_SIZE",))
 
+# python/tutorials/gluon/01-intro.py:84-93 (launch :96-99) and :50-53 (launch :60-63)
+memcpy_kernel = Kernel(
+    "memcpy_kernel", ["in_ptr", "out_ptr", "xnumel", "XBLOCK"], ["*fp32", "*fp32", "i32", "constexpr"], {},
+    spec_keys=("XBLOCK",))
+
+copy_scalar_kernel = Kernel("copy_scalar_kernel", ["in_ptr", "out_ptr"], ["*fp32", "*fp32"], {})
+
 mul_add_kernel = Kernel(
     "mul_add_kernel", ["x_ptr", "y_ptr", "z_ptr", "output_ptr", "n_elements", "BLOCK_SIZE"],
     ["*fp32", "*fp32", "*fp32", "*fp32", "i32", "constexpr"], {}, spec_keys=("BLOCK_SIZE",))

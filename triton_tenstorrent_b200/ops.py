@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["add", "add_loop", "sin", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_tma_host_rows", "matmul_multi", "matmul_fused", "matmul_tma_fused", "attention", "attention_multi",
+__all__ = ["add", "add_loop", "sin", "memcpy", "mul_add", "matmul", "tilize", "untilize", "matmul_tma", "matmul_tma_host_rows", "matmul_multi", "matmul_fused", "matmul_tma_fused", "attention", "attention_multi",
            "attention_with_lse", "attention_backward", "device_status"]
 
 
@@ -124,6 +124,26 @@ def sin(x: torch.Tensor, BLOCK_SIZE: int = 1024) -> torch.Tensor:
     with _on(xd.device):
         _lib.check(lib.b200k_sin_f32(xd.data_ptr(), out.data_ptr(), out.numel(), BLOCK_SIZE, _stream()))
     return _like_input(out, x)
+
+
+def memcpy(input: torch.Tensor, output: torch.Tensor = None, XBLOCK: int = 2048) -> torch.Tensor:
+    """output[i] = input[i] (fp32, bit for bit).  Mirrors memcpy(input, output, XBLOCK), python/tutorials/gluon/01-intro.py:96-99;
+    without `output` a new tensor is returned."""
+    _elementwise_check("memcpy", input)
+    lib = _lib.load()
+    xd = _to_device(input).contiguous()
+    if output is None:
+        out = torch.empty_like(xd)
+    else:
+        if output.dtype != torch.float32 or output.numel() != input.numel() or not output.is_contiguous():
+            raise ValueError("memcpy: output must be a contiguous fp32 tensor with as many elements as input")
+        out = _to_device(output)
+    with _on(xd.device):
+        _lib.check(lib.b200k_copy_f32(xd.data_ptr(), out.data_ptr(), xd.numel(), XBLOCK, _stream()))
+    if output is not None and not output.is_cuda:
+        output.copy_(out)
+        return output
+    return out if output is not None else _like_input(out, input)
 
 
 def mul_add(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, BLOCK_SIZE: int = 1024) -> torch.Tensor:
