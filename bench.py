@@ -275,7 +275,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-workload", default=None,
-                    choices=["matmul", "matmul_fused", "add", "sin", "attention", "attention_causal", "matmul_shard",
+                    choices=["matmul", "matmul_fused", "add", "sin", "memcpy", "attention", "attention_causal", "matmul_shard",
                              "attention_bwd"],
                     help="launch only this kernel warmup+steps times and print nothing to time: the small, "
                          "bounded command the ncu captures summarised under profiles/ are taken from")
@@ -457,10 +457,10 @@ def profile_workload(args, torch, ops, gi):
         bias = torch.randn(4096, device="cuda") * 0.1
         c = torch.empty((16384, 4096), device="cuda", dtype=torch.bfloat16)
         fn = lambda: ops.matmul_fused(a, b, bias, "relu", out=c)
-    elif w in ("add", "sin"):
+    elif w in ("add", "sin", "memcpy"):
         n = 1 << 26
         x, y = torch.rand(n, device="cuda"), torch.rand(n, device="cuda")
-        fn = (lambda: ops.add(x, y)) if w == "add" else (lambda: ops.sin(x))
+        fn = (lambda: ops.add(x, y)) if w == "add" else ((lambda: ops.sin(x)) if w == "sin" else (lambda: ops.memcpy(x, y)))
     elif w == "attention_bwd":
         # half the batch of the attention workload (2 x 32 heads x 4096 x 128): eight tensors of 67 MB, three launches
         q = torch.randn(2, 32, 4096, 128, device="cuda").bfloat16()
